@@ -1,0 +1,799 @@
+// C ABI of libmegaup.so: plans and launches for the two fused Ulysses exchange
+// GEMMs, the cuMem-based symmetric arena, the slot hand-off flag barrier and
+// the layout copies. Declarations and the reference seams they replace are in
+// include/megaup.h.
+//
+// The driver API (cuMem*, cuTensorMapEncodeTiled) is reached through
+// cudaGetDriverEntryPoint, so the library has no link-time dependency on
+// libcuda and can be loaded (symbols inspected) on a machine without a GPU.
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <unistd.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "../../include/megaup.h"
+#include "mup_gemm.cuh"
+
+namespace {
+
+thread_local char g_last_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define MUP_CUDA(expr)                                                                   \
+  do {                                                                                   \
+    cudaError_t e_ = (expr);                                                             \
+    if (e_ != cudaSuccess)                                                               \
+      return fail(MUP_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_),  \
+                  __FILE__, __LINE__);                                                   \
+  } while (0)
+
+// ---------------------------------------------------------------- driver API
+
+struct DriverApi {
+  decltype(&cuTensorMapEncodeTiled) tensor_map_encode_tiled = nullptr;
+  decltype(&cuMemCreate) mem_create = nullptr;
+  decltype(&cuMemRelease) mem_release = nullptr;
+  decltype(&cuMemAddressReserve) mem_address_reserve = nullptr;
+  decltype(&cuMemAddressFree) mem_address_free = nullptr;
+  decltype(&cuMemMap) mem_map = nullptr;
+  decltype(&cuMemUnmap) mem_unmap = nullptr;
+  decltype(&cuMemSetAccess) mem_set_access = nullptr;
+  decltype(&cuMemGetAllocationGranularity) mem_get_granularity = nullptr;
+  decltype(&cuMemExportToShareableHandle) mem_export = nullptr;
+  decltype(&cuMemImportFromShareableHandle) mem_import = nullptr;
+  decltype(&cuGetErrorString) get_error_string = nullptr;
+  bool ok = false;
+  char error[256] = "";
+};
+
+template <typename Fn>
+bool load_entry(const char* name, Fn* out, char* error, size_t error_len) {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult status;
+  cudaError_t e = cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &status);
+  if (e != cudaSuccess || status != cudaDriverEntryPointSuccess || fn == nullptr) {
+    snprintf(error, error_len, "driver entry point %s unavailable (%s)", name,
+             e != cudaSuccess ? cudaGetErrorString(e) : "not found");
+    return false;
+  }
+  *out = reinterpret_cast<Fn>(fn);
+  return true;
+}
+
+const DriverApi& driver() {
+  static DriverApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    bool ok = true;
+    char* err = api.error;
+    const size_t n = sizeof(api.error);
+    ok = ok && load_entry("cuTensorMapEncodeTiled", &api.tensor_map_encode_tiled, err, n);
+    ok = ok && load_entry("cuMemCreate", &api.mem_create, err, n);
+    ok = ok && load_entry("cuMemRelease", &api.mem_release, err, n);
+    ok = ok && load_entry("cuMemAddressReserve", &api.mem_address_reserve, err, n);
+    ok = ok && load_entry("cuMemAddressFree", &api.mem_address_free, err, n);
+    ok = ok && load_entry("cuMemMap", &api.mem_map, err, n);
+    ok = ok && load_entry("cuMemUnmap", &api.mem_unmap, err, n);
+    ok = ok && load_entry("cuMemSetAccess", &api.mem_set_access, err, n);
+    ok = ok && load_entry("cuMemGetAllocationGranularity", &api.mem_get_granularity, err, n);
+    ok = ok && load_entry("cuMemExportToShareableHandle", &api.mem_export, err, n);
+    ok = ok && load_entry("cuMemImportFromShareableHandle", &api.mem_import, err, n);
+    ok = ok && load_entry("cuGetErrorString", &api.get_error_string, err, n);
+    api.ok = ok;
+  });
+  return api;
+}
+
+int driver_fail(const char* what, CUresult r) {
+  const char* msg = nullptr;
+  if (driver().get_error_string != nullptr) driver().get_error_string(r, &msg);
+  return fail(MUP_ERR_DRIVER, "%s failed: %s (CUresult %d)", what, msg ? msg : "?", static_cast<int>(r));
+}
+
+#define MUP_DRV(call, what)                     \
+  do {                                          \
+    CUresult r_ = (call);                       \
+    if (r_ != CUDA_SUCCESS) return driver_fail(what, r_); \
+  } while (0)
+
+// BF16 row-major matrix [outer, inner] -> 2-D tiled tensor map with the
+// 128-byte swizzle; box_inner is always 64 elements (128 bytes).
+int encode_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
+               uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer) {
+  const DriverApi& d = driver();
+  if (!d.ok) return fail(MUP_ERR_DRIVER, "%s", d.error);
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0)
+    return fail(MUP_ERR_BAD_ARG, "tensor base %p is not 16-byte aligned", base);
+  if ((row_stride_elems * 2) % 16 != 0)
+    return fail(MUP_ERR_BAD_ARG, "row stride of %llu BF16 is not a multiple of 16 bytes",
+                static_cast<unsigned long long>(row_stride_elems));
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_elems * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t elem_strides[2] = {1, 1};
+  CUresult r = d.tensor_map_encode_tiled(
+      map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return driver_fail("cuTensorMapEncodeTiled", r);
+  return MUP_OK;
+}
+
+int shape_rule(int64_t width, int up) {
+  if (up != 2 && up != 4 && up != 8) return 1;
+  if (width <= 0 || width % up) return 2;
+  if (width % 256) return 3;
+  if ((width / up) % 128) return 4;
+  return 0;
+}
+
+int n_rotation(int rank, int up, int n_total, int tile_n) {
+  const int n_tiles = (n_total + tile_n - 1) / tile_n;
+  return ((rank * n_tiles + up - 1) / up) % n_tiles;
+}
+
+struct DeviceInfo {
+  int sms = 0;
+  int cc_major = 0;
+};
+
+int query_device(int device, DeviceInfo* info) {
+  MUP_CUDA(cudaDeviceGetAttribute(&info->sms, cudaDevAttrMultiProcessorCount, device));
+  MUP_CUDA(cudaDeviceGetAttribute(&info->cc_major, cudaDevAttrComputeCapabilityMajor, device));
+  return MUP_OK;
+}
+
+template <int G, int MODE>
+int configure_kernel(int* max_clusters) {
+  auto kernel = mup::fused_exchange_gemm_kernel<G, MODE>;
+  const int smem = mup::GemmCfg<G>::kSmemBytes;
+  MUP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  if (G == 2) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(MODE == mup::MODE_PULL ? 256 : 192, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    MUP_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+    *max_clusters = n;
+  }
+  return MUP_OK;
+}
+
+template <int G, int MODE>
+int launch_kernel(const mup::GemmParams& params, int grid, cudaStream_t stream) {
+  auto kernel = mup::fused_exchange_gemm_kernel<G, MODE>;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(MODE == mup::MODE_PULL ? 256 : 192, 1, 1);
+  cfg.dynamicSmemBytes = mup::GemmCfg<G>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = G;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = (G == 2) ? 1 : 0;
+  MUP_CUDA(cudaLaunchKernelEx(&cfg, kernel, params));
+  return MUP_OK;
+}
+
+// Shared plan state of the two operators.
+struct PlanCore {
+  mup::GemmParams params;
+  int device = 0;
+  int cta_group = 1;
+  int grid = 0;
+  int smem_bytes = 0;
+};
+
+int check_common(int device, int rows, int n, int k, int up, int rank, const void* weight,
+                 const void* bias, int cta_group) {
+  if (rows <= 0 || n <= 0 || k <= 0) return fail(MUP_ERR_BAD_ARG, "rows, n and k must be positive");
+  if (up != 2 && up != 4 && up != 8) return fail(MUP_ERR_BAD_ARG, "up must be 2, 4 or 8, got %d", up);
+  if (rank < 0 || rank >= up) return fail(MUP_ERR_BAD_ARG, "rank %d outside [0, %d)", rank, up);
+  if (n % 256) return fail(MUP_ERR_BAD_ARG, "n=%d must be a multiple of 256", n);
+  if (k % 8) return fail(MUP_ERR_BAD_ARG, "k=%d must be a multiple of 8", k);
+  if (weight == nullptr) return fail(MUP_ERR_BAD_ARG, "weight is null");
+  if (bias != nullptr && reinterpret_cast<uintptr_t>(bias) % 16)
+    return fail(MUP_ERR_BAD_ARG, "bias must be 16-byte aligned");
+  if (cta_group < 0 || cta_group > 2) return fail(MUP_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
+  DeviceInfo info;
+  int rc = query_device(device, &info);
+  if (rc != MUP_OK) return rc;
+  if (info.cc_major != 10)
+    return fail(MUP_ERR_UNSUPPORTED, "device %d has compute capability %d.x; sm_100 is required",
+                device, info.cc_major);
+  return MUP_OK;
+}
+
+// Fill the geometry shared by both modes and size the grid.
+template <int MODE>
+int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int rank,
+                int cta_group) {
+  DeviceInfo info;
+  int rc = query_device(device, &info);
+  if (rc != MUP_OK) return rc;
+  const int g = (cta_group == 0) ? 1 : cta_group;
+  mup::GemmParams& p = core->params;
+  p.M = rows;
+  p.N = n;
+  p.K = k;
+  p.up = up;
+  p.rank = rank;
+  p.m_tiles = (rows + mup::kBlockM * g - 1) / (mup::kBlockM * g);
+  p.n_tiles = n / mup::kBlockN;
+  p.k_tiles = (k + mup::kBlockK - 1) / mup::kBlockK;
+  const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
+  int max_clusters = 0;
+  if (g == 1) {
+    rc = configure_kernel<1, MODE>(&max_clusters);
+    if (rc != MUP_OK) return rc;
+    core->grid = static_cast<int>(tiles < info.sms ? tiles : info.sms);
+    core->smem_bytes = mup::GemmCfg<1>::kSmemBytes;
+  } else {
+    rc = configure_kernel<2, MODE>(&max_clusters);
+    if (rc != MUP_OK) return rc;
+    if (max_clusters <= 0) return fail(MUP_ERR_UNSUPPORTED, "no 2-CTA cluster fits on device %d", device);
+    int clusters = info.sms / 2;
+    if (clusters > max_clusters) clusters = max_clusters;
+    if (tiles < clusters) clusters = static_cast<int>(tiles);
+    core->grid = clusters * 2;
+    core->smem_bytes = mup::GemmCfg<2>::kSmemBytes;
+  }
+  core->device = device;
+  core->cta_group = g;
+  return MUP_OK;
+}
+
+}  // namespace
+
+// =========================================================================
+// Plans
+// =========================================================================
+
+struct mup_peer_write_plan {
+  PlanCore core;
+  const void* last_a = nullptr;
+};
+
+struct mup_pull_plan {
+  PlanCore core;
+  void* workspace = nullptr;
+  uint64_t workspace_bytes = 0;
+  unsigned long long launches = 0;
+  unsigned long long pull_warps = 0;
+};
+
+struct mup_arena {
+  CUmemGenericAllocationHandle handle = 0;
+  CUdeviceptr ptr = 0;
+  uint64_t bytes = 0;
+  int fd = -1;
+  int device = 0;
+  bool owner = false;
+};
+
+// =========================================================================
+// Small kernels: flag barrier and layout copies
+// =========================================================================
+
+namespace {
+
+struct FlagParams {
+  uint32_t* flags[mup::kMaxPeers];
+  uint32_t* status;
+  unsigned long long timeout_ns;
+  uint32_t epoch;
+  int up;
+  int rank;
+};
+
+__global__ void flag_barrier_kernel(FlagParams fp) {
+  const int peer = threadIdx.x;
+  if (peer >= fp.up) return;
+  // Everything this GPU wrote before the barrier (including stores to peer
+  // memory by earlier kernels of the stream) is ordered before the flag.
+  mup::fence_acq_rel_sys();
+  mup::st_release_sys(fp.flags[peer] + fp.rank, fp.epoch);
+  const uint32_t* mine = fp.flags[fp.rank] + peer;
+  const uint64_t t0 = mup::globaltimer_ns();
+  uint32_t it = 0;
+  while (static_cast<int32_t>(mup::ld_acquire_sys(mine) - fp.epoch) < 0) {
+    if ((++it & 0x1fu) == 0) {
+      if (mup::globaltimer_ns() - t0 > fp.timeout_ns) {
+        if (fp.status != nullptr) {
+          *reinterpret_cast<volatile uint32_t*>(fp.status) =
+              (mup::ST_FLAG_TIMEOUT << 24) | (static_cast<uint32_t>(peer) & 0xFFFFFFu);
+        }
+        return;
+      }
+      __nanosleep(100);
+    }
+  }
+  mup::fence_acq_rel_sys();
+}
+
+// dst row i <- src row index[i]; rows are `vecs` 16-byte vectors wide.
+__global__ void gather_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                   const int64_t* __restrict__ index, int64_t rows, int64_t vecs) {
+  const int64_t total = rows * vecs;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const int64_t row = i / vecs;
+    const int64_t col = i - row * vecs;
+    const int64_t srow = (index != nullptr) ? index[row] : row;
+    dst[i] = src[srow * vecs + col];
+  }
+}
+
+// Source-major [up, batch, seq] <-> batch-major [batch, up, seq] regroup of rows.
+__global__ void regroup_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int up,
+                                    int batch, int64_t seq, int64_t vecs, int to_batch_major) {
+  const int64_t rows = static_cast<int64_t>(up) * batch * seq;
+  const int64_t total = rows * vecs;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const int64_t row = i / vecs;
+    const int64_t col = i - row * vecs;
+    const int64_t s = row % seq;
+    const int64_t outer = row / seq;
+    int64_t srow;
+    if (to_batch_major) {
+      const int64_t r = outer % up;  // dst row = (b*up + r)*seq + s
+      const int64_t b = outer / up;
+      srow = (r * batch + b) * seq + s;
+    } else {
+      const int64_t b = outer % batch;  // dst row = (r*batch + b)*seq + s
+      const int64_t r = outer / batch;
+      srow = (b * up + r) * seq + s;
+    }
+    dst[i] = src[srow * vecs + col];
+  }
+}
+
+int copy_grid(int64_t total_vecs) {
+  int64_t blocks = (total_vecs + 255) / 256;
+  const int64_t cap = 148 * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks);
+}
+
+}  // namespace
+
+// =========================================================================
+// extern "C"
+// =========================================================================
+
+extern "C" {
+
+int mup_abi_version(void) { return MUP_ABI_VERSION; }
+
+const char* mup_last_error(void) { return g_last_error; }
+
+int mup_device_supported(int device, int* supported) {
+  if (supported == nullptr) return fail(MUP_ERR_BAD_ARG, "supported is null");
+  DeviceInfo info;
+  int rc = query_device(device, &info);
+  if (rc != MUP_OK) return rc;
+  *supported = (info.cc_major == 10) ? 1 : 0;
+  return MUP_OK;
+}
+
+int mup_shape_rule(int64_t width, int up) { return shape_rule(width, up); }
+
+int mup_peer_n_rotation(int rank, int up, int n_total, int tile_n) {
+  if (up <= 0 || n_total <= 0 || tile_n <= 0 || rank < 0) return 0;
+  return n_rotation(rank, up, n_total, tile_n);
+}
+
+// ---------------------------------------------------------------- status
+
+int mup_status_create(uint32_t** host_ptr, void** device_ptr) {
+  if (host_ptr == nullptr || device_ptr == nullptr) return fail(MUP_ERR_BAD_ARG, "null output");
+  void* h = nullptr;
+  MUP_CUDA(cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable));
+  memset(h, 0, 64);
+  void* d = nullptr;
+  MUP_CUDA(cudaHostGetDevicePointer(&d, h, 0));
+  *host_ptr = static_cast<uint32_t*>(h);
+  *device_ptr = d;
+  return MUP_OK;
+}
+
+int mup_status_destroy(uint32_t* host_ptr) {
+  if (host_ptr == nullptr) return MUP_OK;
+  MUP_CUDA(cudaFreeHost(host_ptr));
+  return MUP_OK;
+}
+
+// ---------------------------------------------------------------- arena
+
+int mup_arena_create(int device, uint64_t bytes, mup_arena** out) {
+  if (out == nullptr || bytes == 0) return fail(MUP_ERR_BAD_ARG, "bad arena arguments");
+  const DriverApi& d = driver();
+  if (!d.ok) return fail(MUP_ERR_DRIVER, "%s", d.error);
+  MUP_CUDA(cudaSetDevice(device));
+  MUP_CUDA(cudaFree(nullptr));
+  CUmemAllocationProp prop;
+  memset(&prop, 0, sizeof(prop));
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = device;
+  prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  size_t gran = 0;
+  MUP_DRV(d.mem_get_granularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED),
+          "cuMemGetAllocationGranularity");
+  const uint64_t size = (bytes + gran - 1) / gran * gran;
+  mup_arena* a = new (std::nothrow) mup_arena();
+  if (a == nullptr) return fail(MUP_ERR_BAD_ARG, "out of host memory");
+  a->device = device;
+  a->owner = true;
+  a->bytes = size;
+  CUresult r = d.mem_create(&a->handle, size, &prop, 0);
+  if (r != CUDA_SUCCESS) {
+    delete a;
+    return driver_fail("cuMemCreate", r);
+  }
+  r = d.mem_address_reserve(&a->ptr, size, gran, 0, 0);
+  if (r != CUDA_SUCCESS) {
+    d.mem_release(a->handle);
+    delete a;
+    return driver_fail("cuMemAddressReserve", r);
+  }
+  r = d.mem_map(a->ptr, size, 0, a->handle, 0);
+  if (r != CUDA_SUCCESS) {
+    d.mem_address_free(a->ptr, size);
+    d.mem_release(a->handle);
+    delete a;
+    return driver_fail("cuMemMap", r);
+  }
+  CUmemAccessDesc acc;
+  memset(&acc, 0, sizeof(acc));
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = device;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  r = d.mem_set_access(a->ptr, size, &acc, 1);
+  if (r == CUDA_SUCCESS) {
+    int fd = -1;
+    r = d.mem_export(&fd, a->handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
+    a->fd = fd;
+  }
+  if (r != CUDA_SUCCESS) {
+    d.mem_unmap(a->ptr, size);
+    d.mem_address_free(a->ptr, size);
+    d.mem_release(a->handle);
+    delete a;
+    return driver_fail("cuMemSetAccess/cuMemExportToShareableHandle", r);
+  }
+  cudaError_t e = cudaMemset(reinterpret_cast<void*>(a->ptr), 0, size);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    mup_arena_destroy(a);
+    return fail(MUP_ERR_CUDA, "zero-filling the arena failed: %s", cudaGetErrorString(e));
+  }
+  *out = a;
+  return MUP_OK;
+}
+
+int mup_arena_import(int device, int fd, uint64_t mapped_bytes, mup_arena** out) {
+  if (out == nullptr || fd < 0 || mapped_bytes == 0) return fail(MUP_ERR_BAD_ARG, "bad import arguments");
+  const DriverApi& d = driver();
+  if (!d.ok) return fail(MUP_ERR_DRIVER, "%s", d.error);
+  MUP_CUDA(cudaSetDevice(device));
+  MUP_CUDA(cudaFree(nullptr));
+  mup_arena* a = new (std::nothrow) mup_arena();
+  if (a == nullptr) return fail(MUP_ERR_BAD_ARG, "out of host memory");
+  a->device = device;
+  a->owner = false;
+  a->bytes = mapped_bytes;
+  CUresult r = d.mem_import(&a->handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+                            CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+  if (r != CUDA_SUCCESS) {
+    delete a;
+    return driver_fail("cuMemImportFromShareableHandle", r);
+  }
+  r = d.mem_address_reserve(&a->ptr, mapped_bytes, 0, 0, 0);
+  if (r != CUDA_SUCCESS) {
+    d.mem_release(a->handle);
+    delete a;
+    return driver_fail("cuMemAddressReserve", r);
+  }
+  r = d.mem_map(a->ptr, mapped_bytes, 0, a->handle, 0);
+  if (r != CUDA_SUCCESS) {
+    d.mem_address_free(a->ptr, mapped_bytes);
+    d.mem_release(a->handle);
+    delete a;
+    return driver_fail("cuMemMap", r);
+  }
+  CUmemAccessDesc acc;
+  memset(&acc, 0, sizeof(acc));
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = device;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  r = d.mem_set_access(a->ptr, mapped_bytes, &acc, 1);
+  if (r != CUDA_SUCCESS) {
+    d.mem_unmap(a->ptr, mapped_bytes);
+    d.mem_address_free(a->ptr, mapped_bytes);
+    d.mem_release(a->handle);
+    delete a;
+    return driver_fail("cuMemSetAccess (is peer access available between the two GPUs?)", r);
+  }
+  *out = a;
+  return MUP_OK;
+}
+
+int mup_arena_info(const mup_arena* arena, void** device_ptr, uint64_t* mapped_bytes, int* fd) {
+  if (arena == nullptr) return fail(MUP_ERR_BAD_ARG, "arena is null");
+  if (device_ptr != nullptr) *device_ptr = reinterpret_cast<void*>(arena->ptr);
+  if (mapped_bytes != nullptr) *mapped_bytes = arena->bytes;
+  if (fd != nullptr) *fd = arena->fd;
+  return MUP_OK;
+}
+
+int mup_arena_destroy(mup_arena* arena) {
+  if (arena == nullptr) return MUP_OK;
+  const DriverApi& d = driver();
+  if (d.ok) {
+    if (arena->ptr != 0) {
+      d.mem_unmap(arena->ptr, arena->bytes);
+      d.mem_address_free(arena->ptr, arena->bytes);
+    }
+    if (arena->handle != 0) d.mem_release(arena->handle);
+  }
+  if (arena->owner && arena->fd >= 0) close(arena->fd);
+  delete arena;
+  return MUP_OK;
+}
+
+// ---------------------------------------------------------------- flags
+
+int mup_flag_barrier(void* const* peer_flags, int up, int rank, uint32_t epoch,
+                     void* status_device_ptr, uint64_t timeout_ns, void* stream) {
+  if (peer_flags == nullptr || up < 1 || up > mup::kMaxPeers || rank < 0 || rank >= up)
+    return fail(MUP_ERR_BAD_ARG, "bad flag barrier arguments");
+  FlagParams fp;
+  memset(&fp, 0, sizeof(fp));
+  for (int i = 0; i < up; ++i) {
+    if (peer_flags[i] == nullptr) return fail(MUP_ERR_BAD_ARG, "flag array %d is null", i);
+    fp.flags[i] = static_cast<uint32_t*>(peer_flags[i]);
+  }
+  fp.status = static_cast<uint32_t*>(status_device_ptr);
+  fp.timeout_ns = timeout_ns;
+  fp.epoch = epoch;
+  fp.up = up;
+  fp.rank = rank;
+  flag_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(fp);
+  MUP_CUDA(cudaGetLastError());
+  return MUP_OK;
+}
+
+// ---------------------------------------------------------------- peer write
+
+int mup_peer_write_plan_create(mup_peer_write_plan** out, int device, int rows, int n, int k, int up,
+                               int rank, const void* weight, const void* bias,
+                               void* const* slot_ptrs, int cta_group, void* status_device_ptr,
+                               uint64_t timeout_ns) {
+  if (out == nullptr || slot_ptrs == nullptr) return fail(MUP_ERR_BAD_ARG, "null argument");
+  int rc = check_common(device, rows, n, k, up, rank, weight, bias, cta_group);
+  if (rc != MUP_OK) return rc;
+  if (shape_rule(n, up) != 0)
+    return fail(MUP_ERR_BAD_ARG, "n=%d cannot be exchanged across up=%d ranks (rule %d)", n, up,
+                shape_rule(n, up));
+  mup_peer_write_plan* plan = new (std::nothrow) mup_peer_write_plan();
+  if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "out of host memory");
+  mup::GemmParams& p = plan->core.params;
+  memset(&p, 0, sizeof(p));
+  rc = finish_core<mup::MODE_PEER_WRITE>(&plan->core, device, rows, n, k, up, rank, cta_group);
+  if (rc == MUP_OK) {
+    const int g = plan->core.cta_group;
+    p.shard = n / up;
+    p.n_rot = n_rotation(rank, up, n, mup::kBlockN);
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.status = static_cast<uint32_t*>(status_device_ptr);
+    p.timeout_ns = timeout_ns;
+    rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, mup::kBlockN / g);
+    for (int d = 0; d < up && rc == MUP_OK; ++d) {
+      if (slot_ptrs[d] == nullptr) rc = fail(MUP_ERR_BAD_ARG, "slot pointer %d is null", d);
+      if (rc == MUP_OK)
+        rc = encode_map(&p.map_out[d], slot_ptrs[d], p.shard, rows, p.shard, mup::kEpiCols,
+                        mup::kEpiRows);
+    }
+  }
+  if (rc != MUP_OK) {
+    delete plan;
+    return rc;
+  }
+  *out = plan;
+  return MUP_OK;
+}
+
+int mup_peer_write_launch(mup_peer_write_plan* plan, const void* a, void* stream) {
+  if (plan == nullptr || a == nullptr) return fail(MUP_ERR_BAD_ARG, "null argument");
+  mup::GemmParams& p = plan->core.params;
+  if (a != plan->last_a) {
+    int rc = encode_map(&p.map_a, a, p.K, p.M, p.K, mup::kBlockK, mup::kBlockM);
+    if (rc != MUP_OK) return rc;
+    plan->last_a = a;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (plan->core.cta_group == 2)
+    return launch_kernel<2, mup::MODE_PEER_WRITE>(p, plan->core.grid, s);
+  return launch_kernel<1, mup::MODE_PEER_WRITE>(p, plan->core.grid, s);
+}
+
+int mup_peer_write_plan_info(const mup_peer_write_plan* plan, int* grid_ctas, int* cta_group,
+                             int* n_rotation_out, int* smem_bytes) {
+  if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
+  if (grid_ctas != nullptr) *grid_ctas = plan->core.grid;
+  if (cta_group != nullptr) *cta_group = plan->core.cta_group;
+  if (n_rotation_out != nullptr) *n_rotation_out = plan->core.params.n_rot;
+  if (smem_bytes != nullptr) *smem_bytes = plan->core.smem_bytes;
+  return MUP_OK;
+}
+
+int mup_peer_write_plan_destroy(mup_peer_write_plan* plan) {
+  delete plan;
+  return MUP_OK;
+}
+
+// ---------------------------------------------------------------- pull
+
+uint64_t mup_pull_workspace_bytes(int rows) {
+  if (rows <= 0) return 0;
+  const uint64_t panels = (static_cast<uint64_t>(rows) + mup::kBlockM - 1) / mup::kBlockM;
+  // [0] ticket cursor, [16 ..] per-panel ready counts (cursor on its own 128-byte line)
+  return (16 + panels) * sizeof(unsigned long long);
+}
+
+int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k, int up, int rank,
+                         int peer_rows, const void* weight, const void* bias,
+                         void* const* peer_arena_ptrs, void* dy, void* out_buf, void* workspace,
+                         int cta_group, void* status_device_ptr, uint64_t timeout_ns) {
+  if (out == nullptr || peer_arena_ptrs == nullptr || dy == nullptr || out_buf == nullptr ||
+      workspace == nullptr)
+    return fail(MUP_ERR_BAD_ARG, "null argument");
+  int rc = check_common(device, rows, n, k, up, rank, weight, bias, cta_group);
+  if (rc != MUP_OK) return rc;
+  if (shape_rule(k, up) != 0)
+    return fail(MUP_ERR_BAD_ARG, "k=%d cannot be exchanged across up=%d ranks (rule %d)", k, up,
+                shape_rule(k, up));
+  if (peer_rows < rows) return fail(MUP_ERR_BAD_ARG, "peer_rows=%d < rows=%d", peer_rows, rows);
+  if (reinterpret_cast<uintptr_t>(workspace) % 128)
+    return fail(MUP_ERR_BAD_ARG, "workspace must be 128-byte aligned");
+  mup_pull_plan* plan = new (std::nothrow) mup_pull_plan();
+  if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "out of host memory");
+  mup::GemmParams& p = plan->core.params;
+  memset(&p, 0, sizeof(p));
+  rc = finish_core<mup::MODE_PULL>(&plan->core, device, rows, n, k, up, rank, cta_group);
+  if (rc == MUP_OK) {
+    const int g = plan->core.cta_group;
+    p.shard = k / up;
+    p.n_rot = 0;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.status = static_cast<uint32_t*>(status_device_ptr);
+    p.timeout_ns = timeout_ns;
+    p.dy = static_cast<__nv_bfloat16*>(dy);
+    p.peer_rows = peer_rows;
+    unsigned long long* ws = static_cast<unsigned long long*>(workspace);
+    p.cursor = ws;
+    p.ready = ws + 16;
+    const int groups = (rows + mup::kPullRowsPerTicket - 1) / mup::kPullRowsPerTicket;
+    p.total_tickets = groups * up;
+    for (int i = 0; i < up && rc == MUP_OK; ++i) {
+      if (peer_arena_ptrs[i] == nullptr || reinterpret_cast<uintptr_t>(peer_arena_ptrs[i]) % 16)
+        rc = fail(MUP_ERR_BAD_ARG, "peer arena pointer %d is null or not 16-byte aligned", i);
+      p.peers[i] = static_cast<const __nv_bfloat16*>(peer_arena_ptrs[i]);
+    }
+    if (rc == MUP_OK) rc = encode_map(&p.map_a, dy, k, rows, k, mup::kBlockK, mup::kBlockM);
+    if (rc == MUP_OK) rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, mup::kBlockN / g);
+    if (rc == MUP_OK)
+      rc = encode_map(&p.map_out[0], out_buf, n, rows, n, mup::kEpiCols, mup::kEpiRows);
+    plan->workspace = workspace;
+    plan->workspace_bytes = mup_pull_workspace_bytes(rows);
+    plan->pull_warps = static_cast<unsigned long long>(plan->core.grid) * 2ull;
+  }
+  if (rc != MUP_OK) {
+    delete plan;
+    return rc;
+  }
+  *out = plan;
+  return MUP_OK;
+}
+
+int mup_pull_launch(mup_pull_plan* plan, void* stream) {
+  if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
+  mup::GemmParams& p = plan->core.params;
+  // Every pull warp takes exactly one ticket past the end before it stops,
+  // so a launch advances the cursor by total_tickets + pull_warps.
+  p.epoch1 = plan->launches + 1;
+  p.cursor_base =
+      plan->launches * (static_cast<unsigned long long>(p.total_tickets) + plan->pull_warps);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = (plan->core.cta_group == 2) ? launch_kernel<2, mup::MODE_PULL>(p, plan->core.grid, s)
+                                       : launch_kernel<1, mup::MODE_PULL>(p, plan->core.grid, s);
+  if (rc == MUP_OK) plan->launches += 1;
+  return rc;
+}
+
+int mup_pull_plan_reset(mup_pull_plan* plan, void* stream) {
+  if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
+  MUP_CUDA(cudaMemsetAsync(plan->workspace, 0, plan->workspace_bytes,
+                           static_cast<cudaStream_t>(stream)));
+  plan->launches = 0;
+  return MUP_OK;
+}
+
+int mup_pull_plan_info(const mup_pull_plan* plan, int* grid_ctas, int* cta_group,
+                       uint64_t* launches, int* smem_bytes) {
+  if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
+  if (grid_ctas != nullptr) *grid_ctas = plan->core.grid;
+  if (cta_group != nullptr) *cta_group = plan->core.cta_group;
+  if (launches != nullptr) *launches = plan->launches;
+  if (smem_bytes != nullptr) *smem_bytes = plan->core.smem_bytes;
+  return MUP_OK;
+}
+
+int mup_pull_plan_destroy(mup_pull_plan* plan) {
+  delete plan;
+  return MUP_OK;
+}
+
+// ---------------------------------------------------------------- copies
+
+int mup_gather_rows(void* dst, const void* src, const int64_t* index, int64_t rows,
+                    int64_t row_elems, void* stream) {
+  if (dst == nullptr || src == nullptr || rows <= 0 || row_elems <= 0 || row_elems % 8)
+    return fail(MUP_ERR_BAD_ARG, "bad gather arguments (row_elems must be a multiple of 8)");
+  if (reinterpret_cast<uintptr_t>(dst) % 16 || reinterpret_cast<uintptr_t>(src) % 16)
+    return fail(MUP_ERR_BAD_ARG, "gather buffers must be 16-byte aligned");
+  const int64_t vecs = row_elems / 8;
+  gather_rows_kernel<<<copy_grid(rows * vecs), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(dst), static_cast<const uint4*>(src), index, rows, vecs);
+  MUP_CUDA(cudaGetLastError());
+  return MUP_OK;
+}
+
+int mup_regroup_rows(void* dst, const void* src, int up, int batch, int64_t seq, int64_t row_elems,
+                     int to_batch_major, void* stream) {
+  if (dst == nullptr || src == nullptr || up <= 0 || batch <= 0 || seq <= 0 || row_elems <= 0 ||
+      row_elems % 8)
+    return fail(MUP_ERR_BAD_ARG, "bad regroup arguments (row_elems must be a multiple of 8)");
+  if (reinterpret_cast<uintptr_t>(dst) % 16 || reinterpret_cast<uintptr_t>(src) % 16)
+    return fail(MUP_ERR_BAD_ARG, "regroup buffers must be 16-byte aligned");
+  const int64_t vecs = row_elems / 8;
+  const int64_t total = static_cast<int64_t>(up) * batch * seq * vecs;
+  regroup_rows_kernel<<<copy_grid(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(dst), static_cast<const uint4*>(src), up, batch, seq, vecs,
+      to_batch_major);
+  MUP_CUDA(cudaGetLastError());
+  return MUP_OK;
+}
+
+}  // extern "C"
