@@ -1,0 +1,149 @@
+"""Head-shard pull GEMM: pull warps gather every peer's head shard of each row
+into the dense local input while the MMA warps already consume finished
+128-row panels; ``out = bf16(dy @ W.T + bias)``.
+
+Host handle of ``mup_pull_*`` in libmegaup.so; mirrors the seam of the
+reference's ``mega_up/kernels/headshard_pull_gemm.py``
+(``compile_headshard_pull_gemm`` at :2440-2777, ``CompiledHeadShardPullGemm``
+at :2353-2438). The ticket cursor and the per-panel ready counts only ever
+grow, so launches need no workspace reset in between; ``epoch`` and
+``workspace_epochs`` keep the reference's meaning for callers that recycle.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Sequence
+
+import torch
+from torch import Tensor
+
+from .. import _native
+
+IMPLEMENTATION_REVISION = "megaup-b200-cuda-r1"
+TILE_N = 256
+
+
+class CompiledHeadShardPullGemm:
+    """Bound pull kernel; call it with the stream to launch on."""
+
+    def __init__(
+        self,
+        plan: ctypes.c_void_p,
+        workspace: Tensor,
+        keep_alive: tuple[object, ...],
+        workspace_epochs: int,
+        rows: int,
+        rank: int,
+        up: int,
+    ) -> None:
+        self._plan = plan
+        self._workspace = workspace
+        self._keep_alive = keep_alive
+        self.workspace_epochs = int(workspace_epochs)
+        self.epoch = 0
+        self.logical_m = rows
+        self.rank = rank
+        self.up = up
+        self.tile_n = TILE_N
+        grid, group, smem = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        launches = ctypes.c_uint64()
+        _native.call(
+            "mup_pull_plan_info", plan, ctypes.byref(grid), ctypes.byref(group),
+            ctypes.byref(launches), ctypes.byref(smem),
+        )
+        self.grid_ctas = grid.value
+        self.cta_group = group.value
+        self.smem_bytes = smem.value
+
+    def reset_workspace(self, stream: torch.cuda.Stream | None = None) -> None:
+        """Zero the counters on ``stream`` and restart the launch ordinal."""
+
+        handle = (stream or torch.cuda.current_stream(self._workspace.device)).cuda_stream
+        _native.call("mup_pull_plan_reset", self._plan, handle)
+        self.epoch = 0
+
+    def __call__(self, stream: torch.cuda.Stream | None = None) -> None:
+        if self.epoch >= self.workspace_epochs:
+            raise RuntimeError(
+                "pull workspace exhausted: call reset_workspace() before launching again"
+            )
+        handle = (stream or torch.cuda.current_stream(self._workspace.device)).cuda_stream
+        _native.call("mup_pull_launch", self._plan, handle)
+        self.epoch += 1
+
+    def __del__(self) -> None:
+        plan, self._plan = getattr(self, "_plan", None), None
+        if plan:
+            try:
+                _native.lib().mup_pull_plan_destroy(plan)
+            except Exception:
+                pass
+
+
+def compile_headshard_pull_gemm(
+    peer_addresses: Tensor | Sequence[int],
+    weight: Tensor,
+    out: Tensor,
+    dy: Tensor,
+    *,
+    logical_m: int,
+    rank: int,
+    up: int,
+    bias: Tensor | None = None,
+    workspace_epochs: int = 4096,
+    peer_rows: int | None = None,
+    enable_clc: bool = True,
+    enable_bulk_pull: bool = True,
+    cta_group: int = 0,
+    status_address: int = 0,
+    timeout_ns: int = 5_000_000_000,
+) -> CompiledHeadShardPullGemm:
+    """Bind ``weight [N,K]``, ``bias``, the ``up`` staged peer arenas, the dense
+    input buffer ``dy [rows,K]`` and the output buffer ``out [rows,N]``.
+
+    ``peer_addresses`` holds the base address of every rank's arena (a device
+    uint64 tensor such as ``MegaUPRuntime.peer_address_table``, read back to
+    the host here, or a sequence of ints). ``enable_clc`` and
+    ``enable_bulk_pull`` are accepted for signature compatibility; this
+    kernel has one scheduling and one pull strategy.
+    """
+
+    del enable_clc, enable_bulk_pull
+    device = weight.device
+    if isinstance(peer_addresses, Tensor):
+        addresses = [int(v) for v in peer_addresses.view(torch.int64).tolist()]
+    else:
+        addresses = [int(v) for v in peer_addresses]
+    if len(addresses) != up:
+        raise ValueError(f"expected {up} peer addresses, got {len(addresses)}")
+    rows = int(logical_m)
+    n, k = map(int, weight.shape)
+    for name, tensor, shape in (("weight", weight, (n, k)), ("out", out, (rows, n)), ("dy", dy, (rows, k))):
+        if (
+            tensor.dtype != torch.bfloat16
+            or tensor.device != device
+            or not tensor.is_contiguous()
+            or tuple(tensor.shape) != shape
+        ):
+            raise ValueError(f"{name} must be contiguous BF16 {shape} on {device}")
+    if bias is not None and (
+        bias.dtype != torch.bfloat16 or bias.device != device or tuple(bias.shape) != (n,)
+        or not bias.is_contiguous()
+    ):
+        raise ValueError(f"bias must be contiguous BF16 ({n},) on {device}")
+    if workspace_epochs <= 0:
+        raise ValueError(f"workspace_epochs must be positive, got {workspace_epochs}")
+    nbytes = int(_native.lib().mup_pull_workspace_bytes(rows))
+    workspace = torch.zeros((nbytes + 127) // 128 * 16, dtype=torch.int64, device=device)
+    plan = ctypes.c_void_p()
+    _native.call(
+        "mup_pull_plan_create", ctypes.byref(plan), device.index, rows, n, k, int(up), int(rank),
+        rows if peer_rows is None else int(peer_rows), weight.data_ptr(),
+        None if bias is None else bias.data_ptr(), _native.pointer_array(addresses),
+        dy.data_ptr(), out.data_ptr(), workspace.data_ptr(), int(cta_group),
+        status_address or None, int(timeout_ns),
+    )
+    return CompiledHeadShardPullGemm(
+        plan, workspace, (weight, bias, out, dy), workspace_epochs, rows, int(rank), int(up)
+    )
