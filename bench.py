@@ -1,0 +1,519 @@
+"""Benchmark of the fused Ulysses exchange GEMMs (peer-write Q projection + head-shard
+pull O projection of a Wan2.1-14B-shaped attention block: W[5120,5120] + bias,
+BSHD, B=1, 4096 tokens per rank, H=40, D=128, BF16).
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...        # the unfused CPU path on the host cores
+
+One step = one peer-write call + one pull call of one rank through the
+prepared host API (``validate_group=False``). With N > 1 the Ulysses group is
+the N ranks (UP = N, real peer memory over NVLink); with N = 1 a UP = 8 group
+is emulated on the one GPU (all eight arenas local) and the step is rank 0's.
+Rank 0 prints one JSON line; ``value`` is the whole-job TFLOP/s (sum over the
+GPUs) with inputs resident in HBM, ``e2e`` the same with pinned host inputs
+and outputs copied inside the timed region.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+HIDDEN, HEADS, HEAD_DIM, TOKENS = 5120, 40, 128, 4096
+FLOPS_PER_CALL = 2.0 * TOKENS * HIDDEN * HIDDEN
+NVLINK_BYTES_PER_S = 900e9
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the peer-write
+# kernel at this shape, from the ncu capture summarised under profiles/
+# (None until a capture has been taken).
+PEER_WRITE_DRAM_TRAFFIC_BYTES = None
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+
+
+class ClockSampler:
+    """Sample SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = (
+        "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+        "clocks_event_reasons.sw_power_cap"
+    )
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                     "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=5,
+                ).stdout.strip()
+                if out:
+                    self.samples.append([v.strip() for v in out.splitlines()[0].split(",")])
+            except Exception:  # noqa: BLE001 - clocks are best effort
+                return
+            self._stop.wait(0.1)
+
+    def __enter__(self) -> "ClockSampler":
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self) -> dict:
+        clocks = [int(s[0]) for s in self.samples if s and s[0].isdigit()]
+        maxima = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        reasons = sorted(
+            name for i, name in enumerate(self.NAMES)
+            if any(len(s) > 2 + i and s[2 + i].lower().startswith("active") for s in self.samples)
+        )
+        return {
+            "sm_mhz": int(statistics.median(clocks)) if clocks else None,
+            "sm_max_mhz": max(maxima) if maxima else None,
+            "reasons": reasons,
+            "samples": len(clocks),
+        }
+
+
+# --------------------------------------------------------------------------- CPU legs
+
+
+def cpu_step_rate(budget_s: float, steps: int | None = None, warmup: int = 1) -> dict:
+    """Time the unfused CPU path (oracle/unfused_torch.py) on the host cores; the
+    sample shrinks to a slice of the rows when a full step is too slow."""
+
+    import torch
+
+    from oracle.unfused_torch import UnfusedRank
+
+    rows = TOKENS
+    rank = UnfusedRank(rows, HIDDEN, 8)
+    start = time.perf_counter()
+    rank.step()
+    first = time.perf_counter() - start
+    if first > budget_s / 4 and rows > 256:
+        rows = max(256, int(rows * (budget_s / 8) / first) // 128 * 128)
+        rank = UnfusedRank(rows, HIDDEN, 8)
+        rank.step()
+    for _ in range(max(0, warmup - 1)):
+        rank.step()
+    times = []
+    begin = time.perf_counter()
+    while True:
+        start = time.perf_counter()
+        rank.step()
+        times.append(time.perf_counter() - start)
+        if steps is not None and len(times) >= steps:
+            break
+        if steps is None and (time.perf_counter() - begin > budget_s or len(times) >= 50):
+            break
+    seconds = statistics.median(times)
+    return {
+        "value": rank.flops_per_step / seconds / 1e12,
+        "unit": "TFLOP/s",
+        "cores": torch.get_num_threads(),
+        "kind": "port",
+        "sample": (
+            f"{len(times)} steps of one rank's unfused F.linear + permute + all-to-all copies, "
+            f"{rows} of {TOKENS} rows, W[{HIDDEN},{HIDDEN}] BF16, torch CPU"
+        ),
+        "ms_per_step": seconds * 1e3,
+        "rows": rows,
+    }
+
+
+def run_reference_arm(args) -> None:
+    """The reference's own CPU implementation of the path (its unfused torch path),
+    all host threads, rank 0 only."""
+
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    result = cpu_step_rate(budget_s=60.0, steps=args.steps, warmup=max(1, args.warmup))
+    line = {
+        "impl": "reference",
+        "metric": "fused_proj_a2a_tflops",
+        "value": result["value"],
+        "unit": "TFLOP/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": result["ms_per_step"],
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": workload_config(max(args.gpus, 1)),
+        "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": result["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int) -> dict:
+    up = n_gpus if n_gpus > 1 else 8
+    return {
+        "workload": "Wan2.1-14B-shaped Q projection (peer-write) + O projection (head-shard pull)",
+        "weight": [HIDDEN, HIDDEN],
+        "bias": True,
+        "layout": "BSHD",
+        "batch": 1,
+        "tokens_per_rank": TOKENS,
+        "heads": HEADS,
+        "head_dim": HEAD_DIM,
+        "up": up,
+        "peers": "NVLink peer memory" if n_gpus > 1 else "emulated on one GPU (8 local arenas)",
+        "l2": "per-step working set (2 weights, activations, slots, outputs) is about 360 MB > 126 MB L2",
+    }
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--cta-group", type=int, default=0, help="0 = library default, 1 or 2")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    import megaup_b200 as mega_up
+    from megaup_b200.kernels import headshard_pull_gemm, peer_write_gemm
+
+    if args.cta_group:
+        os.environ["MEGA_UP_CTA_GROUP"] = str(args.cta_group)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != max(args.gpus, 1):
+        raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun), found WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    distributed = world > 1
+    if distributed:
+        dist.init_process_group("nccl", device_id=device)
+        up = world
+        runtime = mega_up.initialize_runtime(dist.group.WORLD, hidden=HIDDEN, max_rows=TOKENS, device=device)
+        runtimes = [runtime]
+    else:
+        up = 8
+        runtimes = list(mega_up.initialize_emulated_group(up, hidden=HIDDEN, max_rows=TOKENS, device=device))
+        runtime = runtimes[0]
+
+    shard = HIDDEN // up
+    gen = torch.Generator(device=device).manual_seed(1234)
+
+    def randn(shape, scale=1.0, generator=gen):
+        return (torch.randn(shape, device=device, generator=generator) * scale).to(torch.bfloat16)
+
+    w_q, w_o = randn((HIDDEN, HIDDEN), HIDDEN ** -0.5), randn((HIDDEN, HIDDEN), HIDDEN ** -0.5)
+    b_q, b_o = randn((HIDDEN,), 0.02), randn((HIDDEN,), 0.02)
+    rank_gen = torch.Generator(device=device).manual_seed(5678 + rank)
+    n_buffers = 3
+    xs = [randn((1, TOKENS, HEADS, HEAD_DIM), generator=rank_gen) for _ in range(n_buffers)]
+    head_xs = [randn((1, up * TOKENS, HEADS // up, HEAD_DIM), generator=rank_gen) for _ in range(n_buffers)]
+    q_out = torch.empty((1, up * TOKENS, HEADS // up, HEAD_DIM), dtype=torch.bfloat16, device=device)
+
+    kw = dict(batch=1, sequence=TOKENS, heads=HEADS, head_dim=HEAD_DIM, validate_group=distributed)
+    peer_write = mega_up.prepare_peer_write_gemm_bshd(w_q, runtime, bias=b_q, **kw)
+    pull = mega_up.prepare_headshard_pull_gemm_bshd(w_o, runtime, bias=b_o, **kw)
+    if not distributed:
+        # the other emulated ranks stage their head-parallel tensors once so that
+        # rank 0's pull reads eight different arenas
+        others = [
+            mega_up.prepare_headshard_pull_gemm_bshd(w_o, rt, bias=b_o, **kw) for rt in runtimes[1:]
+        ]
+        for op in others:
+            op._stage(head_xs[0])
+
+    def step(i: int) -> None:
+        peer_write(xs[i % n_buffers], out=q_out, validate_group=False)
+        pull(head_xs[i % n_buffers], validate_group=False)
+
+    def sync_all() -> None:
+        torch.cuda.synchronize(device)
+        if distributed:
+            dist.barrier()
+            torch.cuda.synchronize(device)
+
+    def rank_max(value: float) -> float:
+        if not distributed:
+            return value
+        t = torch.tensor([value], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- correctness gate before timing (as the reference's bench does): bit-exact vs cuBLAS + torch exchange
+    step(0)
+    torch.cuda.synchronize(device)
+    runtime.check_status()
+    if distributed:
+        dense = F.linear(xs[0].view(TOKENS, HIDDEN), w_q, b_q)
+        send = dense.view(TOKENS, up, shard).permute(1, 0, 2).contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send)
+        gate_pw = torch.equal(q_out.view(up, TOKENS, shard), recv)
+        send = head_xs[0].view(up, TOKENS, shard).contiguous()
+        dist.all_to_all_single(recv, send)
+        mat = recv.permute(1, 0, 2).reshape(TOKENS, HIDDEN).contiguous()
+    else:
+        dense = F.linear(xs[0].view(TOKENS, HIDDEN), w_q, b_q)
+        gate_pw = torch.equal(q_out.view(up, TOKENS, shard)[0], dense[:, :shard])
+        mat = torch.cat([head_xs[0].view(up, TOKENS, shard)[0]] * up, dim=1)
+    gate_pull = torch.equal(pull.materialized_input, mat) and torch.equal(
+        pull.output_2d, F.linear(mat, w_o, b_o)
+    )
+    if not (gate_pw and gate_pull):
+        raise SystemExit(f"correctness gate failed: peer_write={gate_pw} pull={gate_pull}")
+
+    # ---- device-resident timing
+    for i in range(args.warmup):
+        step(i)
+    sync_all()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as sampler:
+        start.record()
+        for i in range(args.steps):
+            step(i)
+        stop.record()
+        sync_all()
+    runtime.check_status()
+    ms_per_step = rank_max(start.elapsed_time(stop) / args.steps)
+    clocks = sampler.summary()
+    total_tflops = world * 2 * FLOPS_PER_CALL / (ms_per_step * 1e-3) / 1e12
+
+    # ---- per-operation and kernel-only timings (CUDA events on the launching stream)
+    def time_us(fn, iters: int) -> float:
+        for i in range(3):
+            fn(i)
+        sync_all()
+        start.record()
+        for i in range(iters):
+            fn(i)
+        stop.record()
+        sync_all()
+        return rank_max(start.elapsed_time(stop) * 1e3 / iters)
+
+    iters = max(args.steps, 10)
+    pw_api_us = time_us(lambda i: peer_write(xs[i % n_buffers], out=q_out, validate_group=False), iters)
+    pull_api_us = time_us(lambda i: pull(head_xs[i % n_buffers], validate_group=False), iters)
+    pw_views = [x.view(TOKENS, HIDDEN) for x in xs]
+    pw_kernel_us = time_us(lambda i: peer_write.launch(pw_views[i % n_buffers]), iters)
+
+    def pull_kernel(i: int) -> None:
+        if pull.compiled.epoch >= pull.compiled.workspace_epochs:
+            pull.compiled.reset_workspace()
+        pull.compiled()
+
+    pull_kernel_us = time_us(pull_kernel, iters)
+    dense_out = torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16, device=device)
+    cublas_us = time_us(lambda i: torch.addmm(b_q, pw_views[i % n_buffers], w_q.t(), out=dense_out), iters)
+
+    # the unfused torch pipeline on the same GPUs (cuBLAS + permute + all_to_all + copy)
+    send = torch.empty((up, TOKENS, shard), dtype=torch.bfloat16, device=device)
+    recv = torch.empty_like(send)
+
+    def unfused(i: int) -> None:
+        torch.addmm(b_q, pw_views[i % n_buffers], w_q.t(), out=dense_out)
+        send.copy_(dense_out.view(TOKENS, up, shard).permute(1, 0, 2))
+        if distributed:
+            dist.all_to_all_single(recv, send)
+        else:
+            recv.copy_(send)
+        q_out.view(up, TOKENS, shard).copy_(recv)
+        send.copy_(head_xs[i % n_buffers].view(up, TOKENS, shard))
+        if distributed:
+            dist.all_to_all_single(recv, send)
+        else:
+            recv.copy_(send)
+        mat.view(TOKENS, up, shard).copy_(recv.permute(1, 0, 2))
+        torch.addmm(b_o, mat, w_o.t(), out=dense_out)
+
+    unfused_us = time_us(unfused, iters)
+
+    # ---- end to end: pinned host inputs in, outputs back out, copies inside the timed region
+    host_x = [torch.empty(x.shape, dtype=torch.bfloat16).pin_memory() for x in xs[:2]]
+    host_hx = [torch.empty(hx.shape, dtype=torch.bfloat16).pin_memory() for hx in head_xs[:2]]
+    for dst, src in zip(host_x + host_hx, xs[:2] + head_xs[:2]):
+        dst.copy_(src)
+    host_q = [torch.empty(q_out.shape, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    host_o = [torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    dev_x = [torch.empty_like(xs[0]) for _ in range(2)]
+    dev_hx = [torch.empty_like(head_xs[0]) for _ in range(2)]
+    dev_q = [torch.empty_like(q_out) for _ in range(2)]
+    dev_o = [torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16, device=device) for _ in range(2)]
+    copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    compute = torch.cuda.current_stream(device)
+    in_done = [torch.cuda.Event() for _ in range(2)]
+    out_done = [torch.cuda.Event() for _ in range(2)]
+    compute_done = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_run(steps: int) -> None:
+        # three-stage pipeline over two buffer sets: H2D(i+1) | compute(i) | D2H(i-1)
+        def upload(i: int) -> None:
+            s = i % 2
+            with torch.cuda.stream(copy_in):
+                copy_in.wait_event(compute_done[s])  # buffer set s is free again
+                dev_x[s].copy_(host_x[s], non_blocking=True)
+                dev_hx[s].copy_(host_hx[s], non_blocking=True)
+                in_done[s].record(copy_in)
+
+        upload(0)
+        for i in range(steps):
+            s = i % 2
+            if i + 1 < steps:
+                upload(i + 1)
+            compute.wait_event(in_done[s])
+            compute.wait_event(out_done[s])  # previous results of set s have left the device
+            peer_write(dev_x[s], out=dev_q[s], validate_group=False)
+            result = pull(dev_hx[s], validate_group=False)
+            dev_o[s].copy_(result.view(TOKENS, HIDDEN))
+            compute_done[s].record(compute)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(compute_done[s])
+                host_q[s].copy_(dev_q[s], non_blocking=True)
+                host_o[s].copy_(dev_o[s], non_blocking=True)
+                out_done[s].record(copy_out)
+
+    for e in compute_done + out_done:
+        e.record(compute)
+    e2e_run(2)
+    sync_all()
+    wall = time.perf_counter()
+    e2e_run(args.steps)
+    sync_all()
+    e2e_ms = rank_max((time.perf_counter() - wall) * 1e3 / args.steps)
+    runtime.check_status()
+    h2d = xs[0].numel() * 2 + head_xs[0].numel() * 2
+    d2h = q_out.numel() * 2 + TOKENS * HIDDEN * 2
+    e2e_ok = torch.equal(host_o[(args.steps - 1) % 2], pull.output_2d.cpu())
+
+    peaks, peak_kind = measured_peaks()
+    burst = float(peaks["bf16_tflops"])
+    exchanged = TOKENS * HIDDEN * 2 * (up - 1) / up
+    roofline_us = max(FLOPS_PER_CALL / (burst * 1e12), exchanged / NVLINK_BYTES_PER_S) * 1e6
+    dominant = "head_shard_pull" if pull_kernel_us >= pw_kernel_us else "peer_write"
+    dominant_us = max(pull_kernel_us, pw_kernel_us)
+
+    if rank == 0:
+        line = {
+            "metric": "fused_proj_a2a_tflops",
+            "value": total_tflops,
+            "unit": "TFLOP/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic",
+            "config": workload_config(world),
+            "per_gpu_tflops": total_tflops / world,
+            "us_per_call": {
+                "peer_write_api": pw_api_us,
+                "pull_api": pull_api_us,
+                "peer_write_kernel": pw_kernel_us,
+                "pull_kernel": pull_kernel_us,
+                "cublas_addmm": cublas_us,
+                "torch_unfused_pipeline_both_ops": unfused_us,
+            },
+            "tflops_per_gpu_per_call": {
+                "peer_write_api": FLOPS_PER_CALL / pw_api_us / 1e6,
+                "pull_api": FLOPS_PER_CALL / pull_api_us / 1e6,
+                "peer_write_kernel": FLOPS_PER_CALL / pw_kernel_us / 1e6,
+                "pull_kernel": FLOPS_PER_CALL / pull_kernel_us / 1e6,
+                "cublas_addmm": FLOPS_PER_CALL / cublas_us / 1e6,
+            },
+            "speedup_vs_torch_unfused": unfused_us / (ms_per_step * 1e3),
+            "per_call_roofline": {
+                "roofline_us": roofline_us,
+                "gemm_us_at_peak": FLOPS_PER_CALL / (burst * 1e12) * 1e6,
+                "nvlink_us": exchanged / NVLINK_BYTES_PER_S * 1e6,
+                "peer_write_kernel_frac": roofline_us / pw_kernel_us,
+                "pull_kernel_frac": roofline_us / pull_kernel_us,
+                "peer_write_api_frac": roofline_us / pw_api_us,
+                "pull_api_frac": roofline_us / pull_api_us,
+            },
+            "roofline": {
+                "bound": "tensor",
+                "kernel": dominant,
+                "achieved": FLOPS_PER_CALL / dominant_us / 1e6,
+                "peak": burst,
+                "unit": "TFLOP/s",
+                "frac": FLOPS_PER_CALL / dominant_us / 1e6 / burst,
+                "traffic": PEER_WRITE_DRAM_TRAFFIC_BYTES,
+                "peak_source": f"{peak_kind} burst bf16 (MEASURED_PEAKS.json)" if peak_kind == "measured" else "fallback",
+                "flops_per_launch": FLOPS_PER_CALL,
+                "us_per_launch": dominant_us,
+            },
+            "e2e": {
+                "value": world * 2 * FLOPS_PER_CALL / (e2e_ms * 1e-3) / 1e12,
+                "unit": "TFLOP/s",
+                "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h,
+                "result_matches_device_run": bool(e2e_ok),
+            },
+            "gpu_launches": args.steps * (4 if not distributed else 8),
+            "kernels": {
+                "cta_group": peer_write.launch.cta_group,
+                "grid_ctas": peer_write.launch.grid_ctas,
+                "revision": peer_write_gemm.IMPLEMENTATION_REVISION,
+                "pull_revision": headshard_pull_gemm.IMPLEMENTATION_REVISION,
+            },
+            "clocks": clocks,
+            "correctness_gate": "bit-exact vs cuBLAS + torch exchange",
+        }
+        if not distributed and not args.no_cpu_baseline:
+            cpu = cpu_step_rate(budget_s=15.0)
+            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

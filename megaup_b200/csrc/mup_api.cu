@@ -237,7 +237,7 @@ int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int 
   DeviceInfo info;
   int rc = query_device(device, &info);
   if (rc != MUP_OK) return rc;
-  const int g = (cta_group == 0) ? 1 : cta_group;
+  const int g = (cta_group == 0) ? 2 : cta_group;  // the CTA pair halves W traffic per SM
   mup::GemmParams& p = core->params;
   p.M = rows;
   p.N = n;

@@ -13,6 +13,7 @@ grow, so launches need no workspace reset in between; ``epoch`` and
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Sequence
 
 import torch
@@ -136,6 +137,8 @@ def compile_headshard_pull_gemm(
         raise ValueError(f"workspace_epochs must be positive, got {workspace_epochs}")
     nbytes = int(_native.lib().mup_pull_workspace_bytes(rows))
     workspace = torch.zeros((nbytes + 127) // 128 * 16, dtype=torch.int64, device=device)
+    if not cta_group:
+        cta_group = int(os.environ.get("MEGA_UP_CTA_GROUP", "0"))
     plan = ctypes.c_void_p()
     _native.call(
         "mup_pull_plan_create", ctypes.byref(plan), device.index, rows, n, k, int(up), int(rank),

@@ -11,6 +11,7 @@ is compiled at run time.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Sequence
 
 import torch
@@ -154,6 +155,8 @@ def make_peer_write_launch(
         start, stop = _span(out)
         if weight_span[0] < stop and start < weight_span[1]:
             raise ValueError("weight overlaps an output slot")
+    if not cta_group:
+        cta_group = int(os.environ.get("MEGA_UP_CTA_GROUP", "0"))
     plan = ctypes.c_void_p()
     _native.call(
         "mup_peer_write_plan_create", ctypes.byref(plan), device.index, rows, n, k, up,

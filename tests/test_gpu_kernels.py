@@ -1,0 +1,220 @@
+"""Parity of the two CUDA kernels, called through the C ABI with emulated peers:
+bit-exact against the CPU oracle on integer-valued inputs (every partial sum
+exact, so the result does not depend on summation order), bit-exact against
+cuBLAS (F.linear on the same GPU) on random inputs wherever cuBLAS does not
+split K, within 1 BF16 ulp where it does."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import _gpu_harness as h
+from oracle import ulysses_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+# (rows, N, K, UP, rank): shapes of the reference's configurations and edge cases
+PEER_SHAPES = [
+    (128, 256, 64, 2, 0),          # one tile, one K step
+    (200, 1024, 1040, 8, 3),       # K % 64 != 0, shard (128) narrower than a tile, ragged M
+    (17, 512, 512, 2, 1),          # fewer rows than one epilogue warp
+    (512, 2304, 2304, 2, 1),       # odd number of 256-column tiles
+    (1024, 2048, 2048, 8, 6),      # LTX-shaped, head_dim 64
+    (64, 1024, 4096, 8, 2),        # Llama-3-8B K projection, small M (cuBLAS splits K)
+    (256, 1536, 1536, 2, 0),       # CPU plumbing configuration of the reference
+    (4096, 5120, 5120, 8, 5),      # Wan2.1-14B Q projection, 640-column shards straddle tiles
+    (4096, 5120, 5120, 4, 3),
+    (4096, 5120, 5120, 2, 1),
+    (8192, 6144, 4096, 8, 7),      # Llama-3-8B fused QKV
+]
+PULL_SHAPES = [
+    (128, 256, 256, 2, 0),
+    (200, 512, 1024, 8, 3),        # shard 128, ragged M
+    (17, 256, 512, 2, 1),
+    (512, 2304, 2304, 2, 0),
+    (1024, 2048, 2048, 8, 6),
+    (4096, 5120, 5120, 8, 5),      # Wan2.1-14B O projection
+    (4096, 5120, 5120, 4, 0),
+    (4096, 5120, 5120, 2, 1),
+    (16384, 8192, 8192, 8, 4),     # Llama-3-70B O projection
+]
+
+
+def _weights(n, k, seed, ints, bias=True):
+    w = h.seeded((n, k), seed, ints=ints, scale=k ** -0.5, lo=-1, hi=2)
+    b = h.seeded((n,), seed + 1, ints=ints, scale=0.02, lo=-3, hi=4) if bias else None
+    return w, b
+
+
+def _oracle_linear(x, w, b, max_rows=1024):
+    """Oracle rows: all of them for small problems, a spread sample otherwise."""
+
+    rows = x.shape[0]
+    pick = np.arange(rows) if rows <= max_rows else np.unique(
+        np.concatenate([np.arange(0, 160), np.arange(rows - 160, rows), np.arange(0, rows, max(1, rows // 640))])
+    )
+    xs = h.to_host(x)[pick]
+    return pick, oracle.linear(xs, h.to_host(w), None if b is None else h.to_host(b), use_c=False)
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("rows,n,k,up,rank", PEER_SHAPES)
+def test_peer_write_kernel(rows, n, k, up, rank, cta_group) -> None:
+    shard = n // up
+    # integer-valued: bit-exact against the CPU oracle, routed per peer_write_route
+    w, b = _weights(n, k, 11, True)
+    x = h.seeded((rows, k), 12, ints=True)
+    slots, guards_clean = h.run_peer_write(x, w, b, up=up, rank=rank, cta_group=cta_group)
+    assert guards_clean, "a store went past the last row"
+    pick, want = _oracle_linear(x, w, b)
+    got = torch.cat(slots, dim=1)
+    assert np.array_equal(h.to_host(got)[pick], want)
+    for col in range(0, n, 64):
+        dst, lcol = oracle.peer_write_route(col, shard)
+        assert torch.equal(slots[dst][:, lcol : lcol + 64], got[:, col : col + 64])
+    # random-valued, with and without bias: bit-exact against cuBLAS
+    for bias in (True, False):
+        w, b = _weights(n, k, 21, False, bias)
+        x = h.seeded((rows, k), 22, ints=False)
+        slots, guards_clean = h.run_peer_write(x, w, b, up=up, rank=rank, cta_group=cta_group)
+        assert guards_clean
+        got = torch.cat(slots, dim=1)
+        ref = F.linear(x, w, b)
+        if torch.equal(got, ref):
+            continue
+        # cuBLAS splits K for small M: then compare with the same rows of a
+        # 4096-row cuBLAS call (bit-exact) and with the small call (<= 1 ulp)
+        assert rows < 256, "cuBLAS and the kernel differ on a large-M problem"
+        padded = torch.zeros((4096, k), device=h.DEVICE, dtype=torch.bfloat16)
+        padded[:rows] = x
+        assert torch.equal(got, F.linear(padded, w, b)[:rows])
+        assert h.ulp_distance(got, ref) <= 1
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("rows,n,k,up,rank", PULL_SHAPES)
+def test_pull_kernel(rows, n, k, up, rank, cta_group) -> None:
+    shard = k // up
+    for ints in (True, False):
+        w, b = _weights(n, k, 31 + ints, ints)
+        peers = [h.seeded((up, rows, shard), 40 + p, ints=ints) for p in range(up)]
+        dy, out, guards_clean = h.run_pull(peers, w, b, rank=rank, cta_group=cta_group, launches=2)
+        assert guards_clean, "a store went past the last row"
+        # the pulled dense input is a pure gather: always bit-exact
+        want_dy = torch.cat([p[rank] for p in peers], dim=1)
+        assert torch.equal(dy, want_dy)
+        if rows <= 4096:
+            host = oracle.pull_gather([h.to_host(p).reshape(-1) for p in peers], rank, rows, shard)
+            assert np.array_equal(h.to_host(dy), host)
+        if ints:
+            pick, want = _oracle_linear(want_dy, w, b)
+            assert np.array_equal(h.to_host(out)[pick], want)
+        else:
+            ref = F.linear(want_dy, w, b)
+            if not torch.equal(out, ref):
+                assert rows < 256
+                assert h.ulp_distance(out, ref) <= 1
+
+
+def test_pull_kernel_is_bit_stable_across_many_launches_under_contention() -> None:
+    """Every launch reuses the same monotonically increasing counters; a side
+    stream keeps SMs busy so CTAs start at different times."""
+
+    rows, n, k, up, rank = 1000, 1024, 2048, 8, 3
+    w, b = _weights(n, k, 51, False)
+    peers = [h.seeded((up, rows, k // up), 60 + p, ints=False) for p in range(up)]
+    side = torch.cuda.Stream()
+    noise = torch.randn(4096, 4096, device=h.DEVICE)
+    with torch.cuda.stream(side):
+        for _ in range(20):
+            noise = torch.nn.functional.gelu(noise @ noise.t() * 1e-3)
+    dy, out, guards_clean = h.run_pull(peers, w, b, rank=rank, cta_group=2, launches=50)
+    side.synchronize()
+    assert guards_clean
+    want_dy = torch.cat([p[rank] for p in peers], dim=1)
+    assert torch.equal(dy, want_dy)
+    assert torch.equal(out, F.linear(want_dy, w, b))
+
+
+def test_layout_copy_kernels() -> None:
+    import ctypes
+
+    from megaup_b200 import _native
+
+    up, batch, seq, shard = 4, 3, 37, 384
+    src = h.seeded((up * batch * seq, shard), 70, ints=False)
+    dst = torch.empty_like(src)
+    _native.call("mup_regroup_rows", dst.data_ptr(), src.data_ptr(), up, batch, seq, shard, 1, h.stream_handle())
+    want = oracle.copy_peer_written(h.to_host(src).reshape(-1), up, batch, seq, shard)
+    assert np.array_equal(h.to_host(dst).reshape(want.shape), want)
+    back = torch.empty_like(src)
+    _native.call("mup_regroup_rows", back.data_ptr(), dst.data_ptr(), up, batch, seq, shard, 0, h.stream_handle())
+    assert torch.equal(back, src)
+    staged = oracle.stage_head_parallel(h.to_host(dst).reshape(batch, up * seq, 1, shard), up)
+    assert np.array_equal(h.to_host(back).reshape(-1), staged)
+    layout = oracle.thd_layout((0, 5, 5, 40, 111), up)
+    index = torch.from_numpy(layout["to_thd_index"]).to(h.DEVICE)
+    gathered = torch.empty_like(src)
+    _native.call("mup_gather_rows", gathered.data_ptr(), src.data_ptr(), index.data_ptr(), src.shape[0], shard, h.stream_handle())
+    torch.cuda.synchronize()
+    assert np.array_equal(h.to_host(gathered), h.to_host(src)[layout["to_thd_index"]])
+    # misaligned buffers and ragged widths are rejected, not truncated
+    lib = _native.lib()
+    assert lib.mup_gather_rows(gathered.data_ptr() + 2, src.data_ptr(), None, 4, shard, None) == -1
+    assert lib.mup_gather_rows(gathered.data_ptr(), src.data_ptr(), None, 4, 12, None) == -1
+
+
+def test_a_flag_nobody_raises_times_out_and_the_context_survives() -> None:
+    """A bounded wait that runs out must end the kernel with a status code."""
+
+    import ctypes
+
+    from megaup_b200 import _native
+
+    flags = [torch.zeros(8, dtype=torch.int32, device=h.DEVICE) for _ in range(2)]
+    status = h.StatusWord()
+    _native.call(
+        "mup_flag_barrier", _native.pointer_array([f.data_ptr() for f in flags]), 2, 0, 1,
+        status.device, 20_000_000, h.stream_handle(),
+    )
+    torch.cuda.synchronize()
+    assert status.value >> 24 == 7 and status.value & 0xFFFFFF == 1  # waited for rank 1
+    assert int(flags[0][0]) == 1 and int(flags[1][0]) == 1  # own arrival was published everywhere
+    # the context is intact: a barrier whose peer has arrived completes
+    status.host[0] = 0
+    flags[0][1] = 2
+    _native.call(
+        "mup_flag_barrier", _native.pointer_array([f.data_ptr() for f in flags]), 2, 0, 2,
+        status.device, 20_000_000, h.stream_handle(),
+    )
+    torch.cuda.synchronize()
+    assert status.value == 0
+    status.close()
+
+
+def test_plan_creation_rejects_what_the_kernels_cannot_run() -> None:
+    import ctypes
+
+    from megaup_b200 import _native
+
+    lib = _native.lib()
+    w = torch.zeros(512, 512, device=h.DEVICE, dtype=torch.bfloat16)
+    slots = [torch.zeros(8, 256, device=h.DEVICE, dtype=torch.bfloat16) for _ in range(2)]
+    ptrs = _native.pointer_array([s.data_ptr() for s in slots])
+    plan = ctypes.c_void_p()
+    args = lambda **kw: (  # noqa: E731
+        ctypes.byref(plan), 0, kw.get("rows", 8), kw.get("n", 512), kw.get("k", 512), kw.get("up", 2),
+        kw.get("rank", 0), w.data_ptr(), kw.get("bias"), ptrs, kw.get("g", 0), None, 1000,
+    )
+    assert lib.mup_peer_write_plan_create(*args(up=3)) == -1
+    assert lib.mup_peer_write_plan_create(*args(n=384)) == -1
+    assert lib.mup_peer_write_plan_create(*args(k=100)) == -1
+    assert lib.mup_peer_write_plan_create(*args(rank=2)) == -1
+    assert lib.mup_peer_write_plan_create(*args(bias=w.data_ptr() + 2)) == -1
+    assert lib.mup_peer_write_plan_create(*args(g=3)) == -1
+    assert lib.mup_peer_write_plan_create(*args()) == 0
+    assert lib.mup_peer_write_launch(plan, w.data_ptr() + 2, None) == -1  # misaligned A
+    lib.mup_peer_write_plan_destroy(plan)
