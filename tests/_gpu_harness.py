@@ -115,11 +115,15 @@ def run_pull(peers, weight, bias, *, rank: int, cta_group: int, launches: int = 
     return dy, out[:rows], bool(torch.isnan(out[rows:]).all())
 
 
-def ulp_distance(a: torch.Tensor, b: torch.Tensor) -> int:
-    """Largest distance in BF16 units in the last place between two BF16 tensors."""
+def ulp_distance(a: torch.Tensor, b: torch.Tensor, floor: float = 2.0 ** -6) -> float:
+    """Largest |a - b| in units of the BF16 ulp at max(|a|, |b|, floor).
 
-    def ordered(t: torch.Tensor) -> torch.Tensor:
-        bits = t.view(torch.int16).to(torch.int32)
-        return torch.where(bits < 0, -(bits & 0x7FFF), bits)
+    Two FP32 sums of the same products in different orders differ by an
+    absolute error, so where the result cancels to (almost) zero the unit is
+    the ulp at ``floor`` rather than the ulp of the tiny result itself.
+    """
 
-    return int((ordered(a) - ordered(b)).abs().max())
+    a32, b32 = a.float(), b.float()
+    scale = torch.maximum(torch.maximum(a32.abs(), b32.abs()), torch.full_like(a32, floor))
+    ulp = torch.exp2(torch.floor(torch.log2(scale)) - 7)
+    return float(((a32 - b32).abs() / ulp).max())

@@ -108,11 +108,11 @@ def main() -> None:
         """Bit-exact, or (where cuBLAS splits K for a small M) within 1 BF16 ulp; on all ranks."""
 
         same = torch.equal(got.reshape(want.shape), want)
-        ulps = 0 if same else ulp_distance(got.reshape(want.shape), want)
-        worst = torch.tensor([ulps], device=device)
+        ulps = 0.0 if same else max(ulp_distance(got.reshape(want.shape), want), 1e-3)
+        worst = torch.tensor([ulps], device=device, dtype=torch.float64)
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-        report["cases"][name] = {"bitwise": int(worst[0]) == 0, "max_ulp": int(worst[0])}
-        if int(worst[0]) > (0 if exact else 1):
+        report["cases"][name] = {"bitwise": float(worst[0]) == 0.0, "max_ulp": round(float(worst[0]), 3)}
+        if float(worst[0]) > (0.0 if exact else 1.0):
             failures.append(name)
 
     heads, dim = 8 * up // 2, 128  # hidden = heads * 128: shards of 4*128 = 512 columns
