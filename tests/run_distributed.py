@@ -31,8 +31,9 @@ from _gpu_harness import ulp_distance  # noqa: E402
 
 
 def a2a(send: torch.Tensor) -> torch.Tensor:
+    send = send.contiguous()
     received = torch.empty_like(send)
-    dist.all_to_all_single(received, send.contiguous())
+    dist.all_to_all_single(received, send)
     return received
 
 
