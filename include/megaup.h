@@ -150,6 +150,42 @@ int mup_pull_plan_info(const mup_pull_plan *plan, int *grid_ctas, int *cta_group
                        uint64_t *launches, int *smem_bytes);
 int mup_pull_plan_destroy(mup_pull_plan *plan);
 
+/* ---- head-shard pull GEMM without any allocation ---------------------------- */
+
+/* Largest `rows` the built-in scratch of mup_pull_gemm_noalloc can serve. */
+#define MUP_NOALLOC_MAX_ROWS 262144
+
+/* One-call variant of the pull GEMM for callers that cannot allocate device
+ * memory at the point of the call: code running under a memory pool that is
+ * already fully committed, inside a framework's "no allocator calls here"
+ * region (for example while another component owns the caching allocator), or
+ * a host that may only hand over buffers it was given. It has no counterpart
+ * in the reference, whose pull always allocates its cursor and ready counts.
+ *
+ * Same computation as mup_pull_plan_create + mup_pull_launch: it fills `dy`
+ * ([rows,k]) from the `up` staged peer arenas and writes
+ * out = bf16(dy @ W^T + bias) to `out_buf` ([rows,n]); the caller still
+ * passes every input and output. What differs is the scratch (ticket cursor
+ * and per-panel ready counts): it is a fixed array inside the library's device
+ * image, about 16 KB per GPU, held by every GPU that loads the library until
+ * the process exits. The call performs no cudaMalloc/cudaFree, creates no
+ * plan object and calls no allocating library routine.
+ *
+ * Limits and rules:
+ *   - rows <= MUP_NOALLOC_MAX_ROWS, otherwise MUP_ERR_BAD_ARG with a message
+ *     naming the limit (use the plan API with your own workspace instead);
+ *   - the first call on a device performs a one-time set-up for that device
+ *     (it resolves the scratch array's device address and sets kernel
+ *     attributes); make that first call before starting any stream capture;
+ *   - all calls on one GPU share the scratch, which keeps the last call's
+ *     contents; each call clears the part it uses on `stream` before the
+ *     kernel. Two calls that overlap on the GPU (different streams without an
+ *     ordering between them) race on it: serialise them. */
+int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, int peer_rows,
+                          const void *weight, const void *bias, void *const *peer_arena_ptrs,
+                          void *dy, void *out_buf, int cta_group, void *status_device_ptr,
+                          uint64_t timeout_ns, void *stream);
+
 /* ---- layout copies ----------------------------------------------------------- */
 
 /* dst row i = src row index[i] (index == NULL: identity), rows of

@@ -77,6 +77,13 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
         (c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_uint64), POINTER(c_int)),
     ),
     "mup_pull_plan_destroy": (c_int, (c_void_p,)),
+    "mup_pull_gemm_noalloc": (
+        c_int,
+        (
+            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+            POINTER(c_void_p), c_void_p, c_void_p, c_int, c_void_p, c_uint64, c_void_p,
+        ),
+    ),
     "mup_gather_rows": (c_int, (c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p)),
     "mup_regroup_rows": (
         c_int,

@@ -765,6 +765,157 @@ int mup_pull_plan_destroy(mup_pull_plan* plan) {
   return MUP_OK;
 }
 
+// ---------------------------------------------------------------- pull without allocation
+
+}  // extern "C" (reopened below; the scratch array and its set-up are file-local)
+
+namespace {
+
+// Scratch of the allocation-free pull entry point: the ticket cursor (word 0)
+// and one ready count per 128-row panel (from word 16). It lives in the
+// library's device image, so every GPU that loads the library holds these
+// bytes until the process exits, and every call on a GPU shares them.
+constexpr int kNoAllocMaxRows = MUP_NOALLOC_MAX_ROWS;
+constexpr int kNoAllocScratchWords = 16 + kNoAllocMaxRows / mup::kBlockM;
+static __device__ __align__(256) unsigned long long g_noalloc_pull_scratch[kNoAllocScratchWords];
+
+constexpr int kNoAllocMaxDevices = 64;
+
+struct NoAllocDevice {
+  bool ready = false;
+  unsigned long long* scratch = nullptr;  // device address of g_noalloc_pull_scratch on this GPU
+  int sms = 0;
+  int max_clusters = 0;  // co-resident 2-CTA clusters of the pull kernel
+};
+
+NoAllocDevice g_noalloc_devices[kNoAllocMaxDevices];
+std::mutex g_noalloc_mutex;
+
+// Once per device, with that device current: resolve the scratch symbol to a
+// device address (in host code the array's name is only a stand-in for it)
+// and raise the kernels' dynamic shared-memory limit.
+int noalloc_setup(int device, const NoAllocDevice** out) {
+  if (device < 0 || device >= kNoAllocMaxDevices)
+    return fail(MUP_ERR_BAD_ARG, "device %d outside [0, %d)", device, kNoAllocMaxDevices);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  NoAllocDevice& slot = g_noalloc_devices[device];
+  if (!slot.ready) {
+    int previous = -1;
+    MUP_CUDA(cudaGetDevice(&previous));
+    if (previous != device) MUP_CUDA(cudaSetDevice(device));
+    void* address = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&address, g_noalloc_pull_scratch);
+    int rc = MUP_OK;
+    if (e != cudaSuccess || address == nullptr) {
+      rc = fail(MUP_ERR_CUDA, "cudaGetSymbolAddress(scratch) failed on device %d: %s", device,
+                cudaGetErrorString(e));
+    }
+    DeviceInfo info;
+    if (rc == MUP_OK) rc = query_device(device, &info);
+    if (rc == MUP_OK && info.cc_major != 10)
+      rc = fail(MUP_ERR_UNSUPPORTED, "device %d has compute capability %d.x; sm_100 is required",
+                device, info.cc_major);
+    int ignored = 0, clusters = 0;
+    if (rc == MUP_OK) rc = configure_kernel<1, mup::MODE_PULL>(&ignored);
+    if (rc == MUP_OK) rc = configure_kernel<2, mup::MODE_PULL>(&clusters);
+    if (previous != device) cudaSetDevice(previous);
+    if (rc != MUP_OK) return rc;
+    slot.scratch = static_cast<unsigned long long*>(address);
+    slot.sms = info.sms;
+    slot.max_clusters = clusters;
+    slot.ready = true;
+  }
+  *out = &slot;
+  return MUP_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, int peer_rows,
+                          const void* weight, const void* bias, void* const* peer_arena_ptrs,
+                          void* dy, void* out_buf, int cta_group, void* status_device_ptr,
+                          uint64_t timeout_ns, void* stream) {
+  if (peer_arena_ptrs == nullptr || dy == nullptr || out_buf == nullptr)
+    return fail(MUP_ERR_BAD_ARG, "null argument");
+  if (rows > kNoAllocMaxRows)
+    return fail(MUP_ERR_BAD_ARG,
+                "rows=%d exceeds MUP_NOALLOC_MAX_ROWS=%d, the capacity of the built-in scratch; "
+                "use mup_pull_plan_create with a caller-provided workspace instead",
+                rows, kNoAllocMaxRows);
+  if (rows <= 0 || n <= 0 || k <= 0) return fail(MUP_ERR_BAD_ARG, "rows, n and k must be positive");
+  if (up != 2 && up != 4 && up != 8) return fail(MUP_ERR_BAD_ARG, "up must be 2, 4 or 8, got %d", up);
+  if (rank < 0 || rank >= up) return fail(MUP_ERR_BAD_ARG, "rank %d outside [0, %d)", rank, up);
+  if (n % 256) return fail(MUP_ERR_BAD_ARG, "n=%d must be a multiple of 256", n);
+  if (shape_rule(k, up) != 0)
+    return fail(MUP_ERR_BAD_ARG, "k=%d cannot be exchanged across up=%d ranks (rule %d)", k, up,
+                shape_rule(k, up));
+  if (weight == nullptr) return fail(MUP_ERR_BAD_ARG, "weight is null");
+  if (bias != nullptr && reinterpret_cast<uintptr_t>(bias) % 16)
+    return fail(MUP_ERR_BAD_ARG, "bias must be 16-byte aligned");
+  if (cta_group < 0 || cta_group > 2) return fail(MUP_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
+  if (peer_rows < rows) return fail(MUP_ERR_BAD_ARG, "peer_rows=%d < rows=%d", peer_rows, rows);
+
+  const NoAllocDevice* dev = nullptr;
+  int rc = noalloc_setup(device, &dev);
+  if (rc != MUP_OK) return rc;
+
+  const int g = (cta_group == 0) ? 2 : cta_group;
+  mup::GemmParams p;  // on the stack: nothing here touches the heap or the device allocator
+  memset(&p, 0, sizeof(p));
+  p.M = rows;
+  p.N = n;
+  p.K = k;
+  p.up = up;
+  p.rank = rank;
+  p.shard = k / up;
+  p.m_tiles = (rows + mup::kBlockM * g - 1) / (mup::kBlockM * g);
+  p.n_tiles = n / mup::kBlockN;
+  p.k_tiles = (k + mup::kBlockK - 1) / mup::kBlockK;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.status = static_cast<uint32_t*>(status_device_ptr);
+  p.timeout_ns = timeout_ns;
+  p.dy = static_cast<__nv_bfloat16*>(dy);
+  p.peer_rows = peer_rows;
+  p.cursor = dev->scratch;
+  p.ready = dev->scratch + 16;
+  p.epoch1 = 1;       // the scratch is cleared below, so every call is "the first launch"
+  p.cursor_base = 0;
+  const int groups = (rows + mup::kPullRowsPerTicket - 1) / mup::kPullRowsPerTicket;
+  p.total_tickets = groups * up;
+  for (int i = 0; i < up; ++i) {
+    if (peer_arena_ptrs[i] == nullptr || reinterpret_cast<uintptr_t>(peer_arena_ptrs[i]) % 16)
+      return fail(MUP_ERR_BAD_ARG, "peer arena pointer %d is null or not 16-byte aligned", i);
+    p.peers[i] = static_cast<const __nv_bfloat16*>(peer_arena_ptrs[i]);
+  }
+  rc = encode_map(&p.map_a, dy, k, rows, k, mup::kBlockK, mup::kBlockM);
+  if (rc == MUP_OK) rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, mup::kBlockN / g);
+  if (rc == MUP_OK) rc = encode_map(&p.map_out[0], out_buf, n, rows, n, mup::kEpiCols, mup::kEpiRows);
+  if (rc != MUP_OK) return rc;
+
+  const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
+  int grid = 0;
+  if (g == 1) {
+    grid = static_cast<int>(tiles < dev->sms ? tiles : dev->sms);
+  } else {
+    if (dev->max_clusters <= 0)
+      return fail(MUP_ERR_UNSUPPORTED, "no 2-CTA cluster fits on device %d", device);
+    int clusters = dev->sms / 2;
+    if (clusters > dev->max_clusters) clusters = dev->max_clusters;
+    if (tiles < clusters) clusters = static_cast<int>(tiles);
+    grid = clusters * 2;
+  }
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps the previous call's counts: the cursor and the ready
+  // counts of the panels this call uses must start at zero.
+  const size_t panels = (static_cast<size_t>(rows) + mup::kBlockM - 1) / mup::kBlockM;
+  MUP_CUDA(cudaMemsetAsync(dev->scratch, 0, (16 + panels) * sizeof(unsigned long long), s));
+  return (g == 2) ? launch_kernel<2, mup::MODE_PULL>(p, grid, s)
+                  : launch_kernel<1, mup::MODE_PULL>(p, grid, s);
+}
+
 // ---------------------------------------------------------------- copies
 
 int mup_gather_rows(void* dst, const void* src, const int64_t* index, int64_t rows,
