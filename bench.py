@@ -375,7 +375,7 @@ def main() -> None:
 
     unfused_us = time_us(unfused, iters)
     # a longer run of the timed step so that the 100 ms clock samples see the GPU under load
-    soak = max(args.steps, int(0.6 / (ms_per_step * 1e-3)))
+    soak = max(args.steps, int(0.6 / (ms_per_step * 1e-3))) if args.steps >= 10 else args.steps
     start.record()
     for i in range(soak):
         step(i)

@@ -123,6 +123,13 @@ int mup_peer_write_plan_create(mup_peer_write_plan **out, int device, int rows, 
 int mup_peer_write_launch(mup_peer_write_plan *plan, const void *a, void *stream);
 int mup_peer_write_plan_info(const mup_peer_write_plan *plan, int *grid_ctas, int *cta_group,
                              int *n_rotation, int *smem_bytes);
+/* Cycle tracing (no counterpart in the reference, which has no built-in tracing):
+ * give the plan a device buffer of grid_ctas * 8 uint64 and every launch
+ * records, per CTA, {start clock, end clock, MMA cycles waiting for operands,
+ * MMA cycles waiting for a free accumulator, TMA-producer cycles waiting for a
+ * free stage, epilogue cycles waiting for an accumulator, start ns, end ns}.
+ * NULL switches tracing off (the default). */
+int mup_peer_write_plan_set_trace(mup_peer_write_plan *plan, void *trace_buffer);
 int mup_peer_write_plan_destroy(mup_peer_write_plan *plan);
 
 /* ---- head-shard pull GEMM --------------------------------------------------- */
@@ -148,6 +155,8 @@ int mup_pull_launch(mup_pull_plan *plan, void *stream);
 int mup_pull_plan_reset(mup_pull_plan *plan, void *stream);
 int mup_pull_plan_info(const mup_pull_plan *plan, int *grid_ctas, int *cta_group,
                        uint64_t *launches, int *smem_bytes);
+/* Same tracing switch as mup_peer_write_plan_set_trace. */
+int mup_pull_plan_set_trace(mup_pull_plan *plan, void *trace_buffer);
 int mup_pull_plan_destroy(mup_pull_plan *plan);
 
 /* ---- head-shard pull GEMM without any allocation ---------------------------- */

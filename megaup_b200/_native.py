@@ -60,6 +60,7 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
         c_int,
         (c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)),
     ),
+    "mup_peer_write_plan_set_trace": (c_int, (c_void_p, c_void_p)),
     "mup_peer_write_plan_destroy": (c_int, (c_void_p,)),
     "mup_pull_workspace_bytes": (c_uint64, (c_int,)),
     "mup_pull_plan_create": (
@@ -76,6 +77,7 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
         c_int,
         (c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_uint64), POINTER(c_int)),
     ),
+    "mup_pull_plan_set_trace": (c_int, (c_void_p, c_void_p)),
     "mup_pull_plan_destroy": (c_int, (c_void_p,)),
     "mup_pull_gemm_noalloc": (
         c_int,

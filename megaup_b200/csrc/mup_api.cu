@@ -13,6 +13,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -266,6 +267,7 @@ int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int 
   }
   core->device = device;
   core->cta_group = g;
+  if (const char* env = getenv("MEGA_UP_KERNEL_FLAGS")) p.flags = static_cast<unsigned int>(atoi(env));
   return MUP_OK;
 }
 
@@ -658,6 +660,13 @@ int mup_peer_write_plan_info(const mup_peer_write_plan* plan, int* grid_ctas, in
   return MUP_OK;
 }
 
+int mup_peer_write_plan_set_trace(mup_peer_write_plan* plan, void* trace_buffer) {
+  if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
+  if (reinterpret_cast<uintptr_t>(trace_buffer) % 8) return fail(MUP_ERR_BAD_ARG, "trace buffer must be 8-byte aligned");
+  plan->core.params.trace = static_cast<unsigned long long*>(trace_buffer);
+  return MUP_OK;
+}
+
 int mup_peer_write_plan_destroy(mup_peer_write_plan* plan) {
   delete plan;
   return MUP_OK;
@@ -757,6 +766,13 @@ int mup_pull_plan_info(const mup_pull_plan* plan, int* grid_ctas, int* cta_group
   if (cta_group != nullptr) *cta_group = plan->core.cta_group;
   if (launches != nullptr) *launches = plan->launches;
   if (smem_bytes != nullptr) *smem_bytes = plan->core.smem_bytes;
+  return MUP_OK;
+}
+
+int mup_pull_plan_set_trace(mup_pull_plan* plan, void* trace_buffer) {
+  if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
+  if (reinterpret_cast<uintptr_t>(trace_buffer) % 8) return fail(MUP_ERR_BAD_ARG, "trace buffer must be 8-byte aligned");
+  plan->core.params.trace = static_cast<unsigned long long*>(trace_buffer);
   return MUP_OK;
 }
 

@@ -99,7 +99,22 @@ struct GemmParams {
   unsigned long long cursor_base;    // cursor value that means "ticket 0" for this launch
   int peer_rows;
   int total_tickets;
+  unsigned int flags;                // tuning switches (kFlag*)
+  unsigned long long* trace;         // optional [grid][8] cycle counters (nullptr: off)
 };
+
+// Per-CTA trace slots (SM cycles unless noted), written when GemmParams::trace is set.
+constexpr int kTraceStart = 0;        // clock64 at kernel entry
+constexpr int kTraceEnd = 1;          // clock64 after the last role finished
+constexpr int kTraceMmaWaitFull = 2;  // MMA thread waiting for operands (TMA behind)
+constexpr int kTraceMmaWaitAcc = 3;   // MMA thread waiting for a free accumulator (epilogue behind)
+constexpr int kTraceProdWait = 4;     // TMA producer waiting for a free stage (MMA behind: the good case)
+constexpr int kTraceEpiWait = 5;      // epilogue warp 2 waiting for a finished accumulator
+constexpr int kTraceNsStart = 6;      // %globaltimer at entry
+constexpr int kTraceNsEnd = 7;        // %globaltimer at exit
+constexpr int kTraceSlots = 8;
+
+constexpr unsigned int kFlagPairCommit = 1u;  // G=2: one commit to both CTAs instead of one per CTA
 
 __device__ __forceinline__ void report_status(const GemmParams& p, volatile uint32_t* abort_flag,
                                               uint32_t code, uint32_t detail) {
@@ -131,6 +146,11 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Cfg::kOffTmemSlot);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + Cfg::kOffAbort);
   const uint64_t timeout_ns = p.timeout_ns;
+  unsigned long long* trace = (p.trace != nullptr) ? p.trace + static_cast<size_t>(blockIdx.x) * kTraceSlots : nullptr;
+  if (trace != nullptr && threadIdx.x == 0) {
+    trace[kTraceStart] = clock64();
+    trace[kTraceNsStart] = globaltimer_ns();
+  }
 
   // ------------------------------------------------------------------ set-up
   if (threadIdx.x == 0) {
@@ -170,6 +190,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t stage = 0, phase = 0;
       uint32_t in_flight = 0;  // loads armed so far (saturates at kStages)
       bool ok = true;
+      long long waited = 0;
       const uint32_t leader_full0 = (G == 2) ? mapa_cluster(full_bar(0), 0) : full_bar(0);
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const int m_idx = tile / p.n_tiles;
@@ -205,7 +226,10 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
         }
         for (int kt = 0; kt < p.k_tiles; ++kt) {
-          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, timeout_ns)) {
+          const long long t_wait = trace ? clock64() : 0;
+          const bool free_stage = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, timeout_ns);
+          if (trace) waited += clock64() - t_wait;
+          if (!free_stage) {
             report_status(p, abort_flag, ST_PRODUCER_SLOT_TIMEOUT, static_cast<uint32_t>(tile));
             ok = false;
             break;
@@ -231,6 +255,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
         }
       }
+      if (trace) trace[kTraceProdWait] = static_cast<unsigned long long>(waited);
       if (!ok && G == 1) {
         // Giving up: let loads that are still in flight land before the CTA
         // retires (their barrier completes without any consumer).
@@ -256,10 +281,14 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t stage = 0, phase = 0;
       uint32_t acc_it = 0;
       bool ok = true;
+      long long wait_full = 0, wait_acc = 0;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++acc_it) {
         const uint32_t as = acc_it & 1u;
         const uint32_t aphase = (acc_it >> 1) & 1u;
-        if (!mbar_wait_bounded(acc_empty_bar(as), aphase ^ 1u, abort_flag, timeout_ns)) {
+        const long long t_acc = trace ? clock64() : 0;
+        const bool acc_free = mbar_wait_bounded(acc_empty_bar(as), aphase ^ 1u, abort_flag, timeout_ns);
+        if (trace) wait_acc += clock64() - t_acc;
+        if (!acc_free) {
           report_status(p, abort_flag, ST_MMA_ACC_TIMEOUT, static_cast<uint32_t>(tile));
           ok = false;
           break;
@@ -267,7 +296,10 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + as * kBlockN;
         for (int kt = 0; kt < p.k_tiles; ++kt) {
-          if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, timeout_ns)) {
+          const long long t_full = trace ? clock64() : 0;
+          const bool filled = mbar_wait_bounded(full_bar(stage), phase, abort_flag, timeout_ns);
+          if (trace) wait_full += clock64() - t_full;
+          if (!filled) {
             report_status(p, abort_flag, ST_MMA_FULL_TIMEOUT, static_cast<uint32_t>(tile));
             ok = false;
             break;
@@ -286,6 +318,8 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           // Release the shared-memory slot once these MMAs have read it.
           if constexpr (G == 1) {
             umma_commit_1(empty_bar(stage));
+          } else if (p.flags & kFlagPairCommit) {
+            umma_commit_2_mask(empty_bar(stage), 3);
           } else {
             umma_commit_2(mapa_cluster(empty_bar(stage), 0));
             umma_commit_2(mapa_cluster(empty_bar(stage), 1));
@@ -299,10 +333,16 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         // Publish the finished accumulator to the epilogue warps.
         if constexpr (G == 1) {
           umma_commit_1(acc_full_bar(as));
+        } else if (p.flags & kFlagPairCommit) {
+          umma_commit_2_mask(acc_full_bar(as), 3);
         } else {
           umma_commit_2(mapa_cluster(acc_full_bar(as), 0));
           umma_commit_2(mapa_cluster(acc_full_bar(as), 1));
         }
+      }
+      if (trace) {
+        trace[kTraceMmaWaitFull] = static_cast<unsigned long long>(wait_full);
+        trace[kTraceMmaWaitAcc] = static_cast<unsigned long long>(wait_acc);
       }
     }
   }
@@ -317,6 +357,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     uint32_t acc_it = 0;
     uint32_t store_it = 0;
     bool ok = true;
+    long long epi_wait = 0;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++acc_it) {
       const int m_idx = tile / p.n_tiles;
       const int n_idx = tile - m_idx * p.n_tiles;
@@ -326,7 +367,9 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t aphase = (acc_it >> 1) & 1u;
       const int row0 = (m_idx * G + static_cast<int>(cta_rank)) * kBlockM + q * kEpiRows;
 
+      const long long t_epi = trace ? clock64() : 0;
       const bool got = mbar_wait_bounded(acc_full_bar(as), aphase, abort_flag, timeout_ns);
+      if (trace) epi_wait += clock64() - t_epi;
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) report_status(p, abort_flag, ST_EPILOGUE_TIMEOUT, static_cast<uint32_t>(tile));
         ok = false;
@@ -415,6 +458,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     // before the kernel ends and the hand-off flag is raised.
     if (lane == 0) bulk_wait_group<0>();
     __syncwarp();
+    if (trace && warp == 2 && lane == 0) trace[kTraceEpiWait] = static_cast<unsigned long long>(epi_wait);
   }
 
   // ------------------------------------------------------------ pull workers
@@ -484,6 +528,10 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc<G>(tmem_base, kTmemCols);
+  }
+  if (trace != nullptr && threadIdx.x == 0) {
+    trace[kTraceEnd] = clock64();
+    trace[kTraceNsEnd] = globaltimer_ns();
   }
 }
 

@@ -253,6 +253,15 @@ __device__ __forceinline__ void umma_commit_2(uint32_t cluster_bar) {
       : "memory");
 }
 
+// One commit delivered to the barrier at the same shared-memory offset in
+// every CTA named by `cta_mask` (an mbarrier arrival, not a data load).
+__device__ __forceinline__ void umma_commit_2_mask(uint32_t bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(cta_mask)
+      : "memory");
+}
+
 // 32 lanes x 32 consecutive FP32 columns: thread t of the warp receives row
 // (lane quarter base + t), registers = columns.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
