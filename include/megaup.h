@@ -121,13 +121,16 @@ int mup_peer_write_plan_create(mup_peer_write_plan **out, int device, int rows, 
 /* Launch on `stream` for input `a` ([rows, k] BF16, 16-byte aligned).
  * Replaces PeerWriteLaunch.__call__ (peer_write_gemm.py:2677-2694). */
 int mup_peer_write_launch(mup_peer_write_plan *plan, const void *a, void *stream);
+/* Any output pointer may be NULL. tile_n is the width of an output tile the
+ * library chose for this problem (128, 192 or 256 columns). */
 int mup_peer_write_plan_info(const mup_peer_write_plan *plan, int *grid_ctas, int *cta_group,
-                             int *n_rotation, int *smem_bytes);
+                             int *n_rotation, int *smem_bytes, int *tile_n);
 /* Cycle tracing (no counterpart in the reference, which has no built-in tracing):
- * give the plan a device buffer of grid_ctas * 8 uint64 and every launch
+ * give the plan a zeroed device buffer of grid_ctas * 16 uint64 and every launch
  * records, per CTA, {start clock, end clock, MMA cycles waiting for operands,
  * MMA cycles waiting for a free accumulator, TMA-producer cycles waiting for a
- * free stage, epilogue cycles waiting for an accumulator, start ns, end ns}.
+ * free stage, epilogue cycles waiting for an accumulator, start ns, end ns,
+ * end ns of the CTA's pull workers, tickets they copied} (unused slots stay 0).
  * NULL switches tracing off (the default). */
 int mup_peer_write_plan_set_trace(mup_peer_write_plan *plan, void *trace_buffer);
 int mup_peer_write_plan_destroy(mup_peer_write_plan *plan);
@@ -154,7 +157,7 @@ int mup_pull_launch(mup_pull_plan *plan, void *stream);
  * CompiledHeadShardPullGemm.reset_workspace (headshard_pull_gemm.py:2393-2405). */
 int mup_pull_plan_reset(mup_pull_plan *plan, void *stream);
 int mup_pull_plan_info(const mup_pull_plan *plan, int *grid_ctas, int *cta_group,
-                       uint64_t *launches, int *smem_bytes);
+                       uint64_t *launches, int *smem_bytes, int *tile_n);
 /* Same tracing switch as mup_peer_write_plan_set_trace. */
 int mup_pull_plan_set_trace(mup_pull_plan *plan, void *trace_buffer);
 int mup_pull_plan_destroy(mup_pull_plan *plan);

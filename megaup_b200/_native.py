@@ -58,7 +58,7 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
     "mup_peer_write_launch": (c_int, (c_void_p, c_void_p, c_void_p)),
     "mup_peer_write_plan_info": (
         c_int,
-        (c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)),
+        (c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)),
     ),
     "mup_peer_write_plan_set_trace": (c_int, (c_void_p, c_void_p)),
     "mup_peer_write_plan_destroy": (c_int, (c_void_p,)),
@@ -75,7 +75,7 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
     "mup_pull_plan_reset": (c_int, (c_void_p, c_void_p)),
     "mup_pull_plan_info": (
         c_int,
-        (c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_uint64), POINTER(c_int)),
+        (c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_uint64), POINTER(c_int), POINTER(c_int)),
     ),
     "mup_pull_plan_set_trace": (c_int, (c_void_p, c_void_p)),
     "mup_pull_plan_destroy": (c_int, (c_void_p,)),

@@ -133,6 +133,21 @@ int encode_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t oute
   return MUP_OK;
 }
 
+// Rows per pull ticket: the largest power of two (at most 16) whose shard rows
+// fit one batch of 512 sixteen-byte peer loads per warp.
+int pull_rows_for(int shard) {
+  if (const char* env = getenv("MEGA_UP_PULL_ROWS")) {
+    const int forced = atoi(env);
+    if ((forced == 1 || forced == 2 || forced == 4 || forced == 8 || forced == 16) &&
+        forced * (shard / 8) <= mup::kPullMaxVecs)
+      return forced;
+  }
+  const int vec_per_row = shard / 8;
+  int rows = 16;
+  while (rows > 1 && rows * vec_per_row > mup::kPullMaxVecs) rows /= 2;
+  return rows;
+}
+
 int shape_rule(int64_t width, int up) {
   if (up != 2 && up != 4 && up != 8) return 1;
   if (width <= 0 || width % up) return 2;
@@ -166,7 +181,7 @@ int configure_kernel(int* max_clusters) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(2, 1, 1);
-    cfg.blockDim = dim3(MODE == mup::MODE_PULL ? 256 : 192, 1, 1);
+    cfg.blockDim = dim3(mup::kernel_threads(MODE), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -188,7 +203,7 @@ int launch_kernel(const mup::GemmParams& params, int grid, cudaStream_t stream) 
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(MODE == mup::MODE_PULL ? 256 : 192, 1, 1);
+  cfg.blockDim = dim3(mup::kernel_threads(MODE), 1, 1);
   cfg.dynamicSmemBytes = mup::GemmCfg<G>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr;
@@ -231,6 +246,32 @@ int check_common(int device, int rows, int n, int k, int up, int rank, const voi
   return MUP_OK;
 }
 
+// Width of an output tile. A tcgen05.mma of M = 128 rows per SM occupies the
+// tensor pipe for 128 cycles whatever its N (measured: 256, 192, 128 and 64
+// columns all take 128 cycles), so a narrower tile only pays off when it
+// lowers the number of waves; ties go to the widest tile.
+// MEGA_UP_TILE_N overrides the choice (tuning only).
+int choose_tile_n(int m_tiles, int n, int slots) {
+  if (const char* env = getenv("MEGA_UP_TILE_N")) {
+    const int forced = atoi(env);
+    if (forced == 128 || forced == 192 || forced == 256) return forced;
+  }
+  const int candidates[3] = {256, 192, 128};
+  int best = 256;
+  long long best_cost = -1;
+  for (int c = 0; c < 3; ++c) {
+    const int t = candidates[c];
+    const long long tiles = static_cast<long long>(m_tiles) * ((n + t - 1) / t);
+    const long long waves = (tiles + slots - 1) / slots;
+    const long long cost = waves;
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = t;
+    }
+  }
+  return best;
+}
+
 // Fill the geometry shared by both modes and size the grid.
 template <int MODE>
 int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int rank,
@@ -246,13 +287,14 @@ int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int 
   p.up = up;
   p.rank = rank;
   p.m_tiles = (rows + mup::kBlockM * g - 1) / (mup::kBlockM * g);
-  p.n_tiles = n / mup::kBlockN;
   p.k_tiles = (k + mup::kBlockK - 1) / mup::kBlockK;
-  const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
   int max_clusters = 0;
   if (g == 1) {
     rc = configure_kernel<1, MODE>(&max_clusters);
     if (rc != MUP_OK) return rc;
+    p.tile_n = choose_tile_n(p.m_tiles, n, info.sms);
+    p.n_tiles = (n + p.tile_n - 1) / p.tile_n;
+    const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
     core->grid = static_cast<int>(tiles < info.sms ? tiles : info.sms);
     core->smem_bytes = mup::GemmCfg<1>::kSmemBytes;
   } else {
@@ -261,6 +303,9 @@ int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int 
     if (max_clusters <= 0) return fail(MUP_ERR_UNSUPPORTED, "no 2-CTA cluster fits on device %d", device);
     int clusters = info.sms / 2;
     if (clusters > max_clusters) clusters = max_clusters;
+    p.tile_n = choose_tile_n(p.m_tiles, n, clusters);
+    p.n_tiles = (n + p.tile_n - 1) / p.tile_n;
+    const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
     if (tiles < clusters) clusters = static_cast<int>(tiles);
     core->grid = clusters * 2;
     core->smem_bytes = mup::GemmCfg<2>::kSmemBytes;
@@ -616,11 +661,11 @@ int mup_peer_write_plan_create(mup_peer_write_plan** out, int device, int rows, 
   if (rc == MUP_OK) {
     const int g = plan->core.cta_group;
     p.shard = n / up;
-    p.n_rot = n_rotation(rank, up, n, mup::kBlockN);
+    p.n_rot = n_rotation(rank, up, n, p.tile_n);
     p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.status = static_cast<uint32_t*>(status_device_ptr);
     p.timeout_ns = timeout_ns;
-    rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, mup::kBlockN / g);
+    rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, p.tile_n / g);
     for (int d = 0; d < up && rc == MUP_OK; ++d) {
       if (slot_ptrs[d] == nullptr) rc = fail(MUP_ERR_BAD_ARG, "slot pointer %d is null", d);
       if (rc == MUP_OK)
@@ -651,7 +696,8 @@ int mup_peer_write_launch(mup_peer_write_plan* plan, const void* a, void* stream
 }
 
 int mup_peer_write_plan_info(const mup_peer_write_plan* plan, int* grid_ctas, int* cta_group,
-                             int* n_rotation_out, int* smem_bytes) {
+                             int* n_rotation_out, int* smem_bytes, int* tile_n) {
+  if (plan != nullptr && tile_n != nullptr) *tile_n = plan->core.params.tile_n;
   if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
   if (grid_ctas != nullptr) *grid_ctas = plan->core.grid;
   if (cta_group != nullptr) *cta_group = plan->core.cta_group;
@@ -713,7 +759,8 @@ int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k
     unsigned long long* ws = static_cast<unsigned long long*>(workspace);
     p.cursor = ws;
     p.ready = ws + 16;
-    const int groups = (rows + mup::kPullRowsPerTicket - 1) / mup::kPullRowsPerTicket;
+    p.pull_rows = pull_rows_for(p.shard);
+    const int groups = (rows + p.pull_rows - 1) / p.pull_rows;
     p.total_tickets = groups * up;
     for (int i = 0; i < up && rc == MUP_OK; ++i) {
       if (peer_arena_ptrs[i] == nullptr || reinterpret_cast<uintptr_t>(peer_arena_ptrs[i]) % 16)
@@ -721,12 +768,13 @@ int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k
       p.peers[i] = static_cast<const __nv_bfloat16*>(peer_arena_ptrs[i]);
     }
     if (rc == MUP_OK) rc = encode_map(&p.map_a, dy, k, rows, k, mup::kBlockK, mup::kBlockM);
-    if (rc == MUP_OK) rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, mup::kBlockN / g);
+    if (rc == MUP_OK) rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, p.tile_n / g);
     if (rc == MUP_OK)
       rc = encode_map(&p.map_out[0], out_buf, n, rows, n, mup::kEpiCols, mup::kEpiRows);
     plan->workspace = workspace;
     plan->workspace_bytes = mup_pull_workspace_bytes(rows);
-    plan->pull_warps = static_cast<unsigned long long>(plan->core.grid) * 2ull;
+    plan->pull_warps = static_cast<unsigned long long>(plan->core.grid) * mup::kPullWarps;
+    p.pull_stride = static_cast<int>(plan->pull_warps);
   }
   if (rc != MUP_OK) {
     delete plan;
@@ -739,11 +787,16 @@ int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k
 int mup_pull_launch(mup_pull_plan* plan, void* stream) {
   if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
   mup::GemmParams& p = plan->core.params;
-  // Every pull warp takes exactly one ticket past the end before it stops,
-  // so a launch advances the cursor by total_tickets + pull_warps.
+  // Tickets are drawn in chunks; every pull warp draws exactly one chunk past
+  // the end before it stops, so a launch advances the cursor by chunks + pull_warps.
+  const unsigned long long block = plan->pull_warps * mup::kPullChunk;
+  const unsigned long long chunks =
+      (static_cast<unsigned long long>(p.total_tickets) + block - 1) / block * plan->pull_warps;
+  // Chunks 0 .. pull_warps-1 are pre-assigned (one per pull warp), the cursor
+  // hands out chunks pull_warps .. chunks-1 and one miss per warp.
+  const unsigned long long drawn = (chunks > plan->pull_warps ? chunks - plan->pull_warps : 0ull);
   p.epoch1 = plan->launches + 1;
-  p.cursor_base =
-      plan->launches * (static_cast<unsigned long long>(p.total_tickets) + plan->pull_warps);
+  p.cursor_base = plan->launches * (drawn + plan->pull_warps);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int rc = (plan->core.cta_group == 2) ? launch_kernel<2, mup::MODE_PULL>(p, plan->core.grid, s)
                                        : launch_kernel<1, mup::MODE_PULL>(p, plan->core.grid, s);
@@ -760,7 +813,8 @@ int mup_pull_plan_reset(mup_pull_plan* plan, void* stream) {
 }
 
 int mup_pull_plan_info(const mup_pull_plan* plan, int* grid_ctas, int* cta_group,
-                       uint64_t* launches, int* smem_bytes) {
+                       uint64_t* launches, int* smem_bytes, int* tile_n) {
+  if (plan != nullptr && tile_n != nullptr) *tile_n = plan->core.params.tile_n;
   if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
   if (grid_ctas != nullptr) *grid_ctas = plan->core.grid;
   if (cta_group != nullptr) *cta_group = plan->core.cta_group;
@@ -887,7 +941,16 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
   p.rank = rank;
   p.shard = k / up;
   p.m_tiles = (rows + mup::kBlockM * g - 1) / (mup::kBlockM * g);
-  p.n_tiles = n / mup::kBlockN;
+  {
+    int slots = dev->sms;
+    if (g == 2) {
+      slots = dev->sms / 2;
+      if (slots > dev->max_clusters) slots = dev->max_clusters;
+      if (slots <= 0) return fail(MUP_ERR_UNSUPPORTED, "no 2-CTA cluster fits on device %d", device);
+    }
+    p.tile_n = choose_tile_n(p.m_tiles, n, slots);
+  }
+  p.n_tiles = (n + p.tile_n - 1) / p.tile_n;
   p.k_tiles = (k + mup::kBlockK - 1) / mup::kBlockK;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.status = static_cast<uint32_t*>(status_device_ptr);
@@ -898,7 +961,8 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
   p.ready = dev->scratch + 16;
   p.epoch1 = 1;       // the scratch is cleared below, so every call is "the first launch"
   p.cursor_base = 0;
-  const int groups = (rows + mup::kPullRowsPerTicket - 1) / mup::kPullRowsPerTicket;
+  p.pull_rows = pull_rows_for(p.shard);
+  const int groups = (rows + p.pull_rows - 1) / p.pull_rows;
   p.total_tickets = groups * up;
   for (int i = 0; i < up; ++i) {
     if (peer_arena_ptrs[i] == nullptr || reinterpret_cast<uintptr_t>(peer_arena_ptrs[i]) % 16)
@@ -906,7 +970,7 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
     p.peers[i] = static_cast<const __nv_bfloat16*>(peer_arena_ptrs[i]);
   }
   rc = encode_map(&p.map_a, dy, k, rows, k, mup::kBlockK, mup::kBlockM);
-  if (rc == MUP_OK) rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, mup::kBlockN / g);
+  if (rc == MUP_OK) rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, p.tile_n / g);
   if (rc == MUP_OK) rc = encode_map(&p.map_out[0], out_buf, n, rows, n, mup::kEpiCols, mup::kEpiRows);
   if (rc != MUP_OK) return rc;
 
@@ -923,6 +987,7 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
     grid = clusters * 2;
   }
 
+  p.pull_stride = grid * mup::kPullWarps;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // The array keeps the previous call's counts: the cursor and the ready
   // counts of the panels this call uses must start at zero.

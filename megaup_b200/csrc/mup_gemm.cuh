@@ -18,11 +18,11 @@
 // receives the K products in ascending order, 16 at a time; bias is added in
 // FP32 and the sum is rounded to BF16 once.
 //
-// Warp roles (192 threads, 256 in pull mode):
+// Warp roles (192 threads, 384 in pull mode):
 //   warp 0      TMA producer (one elected lane)
-//   warp 1      TMEM allocation + MMA issue (one elected lane, leader CTA)
+//   warp 1      TMEM allocation + MMA issue (warp-uniform loop, one elected lane issues; leader CTA)
 //   warps 2-5   epilogue; warp w owns TMEM lanes 32*(w%4) .. +31
-//   warps 6-7   (pull mode) peer -> dy copy workers
+//   warps 6-11  (pull mode) peer -> dy copy workers
 //
 // Every wait is bounded. A role that gives up records a code in *status,
 // raises the CTA's abort flag so the other roles give up too, and all roles
@@ -44,8 +44,10 @@ constexpr int kEpiCols = 64;        // columns per epilogue sub-tile (128 bytes)
 constexpr int kEpiRows = 32;        // rows per epilogue warp
 constexpr int kEpiBufBytes = kEpiRows * kEpiCols * 2;  // 4096
 constexpr int kEpiBufs = 2;
-constexpr int kPullRowsPerTicket = 16;
-constexpr int kPullUnroll = 8;
+constexpr int kPullMaxVecs = 512;     // 16-byte vectors per pull ticket (one batch of peer loads per warp)
+constexpr int kPullUnroll = kPullMaxVecs / 32;
+constexpr int kPullWarps = 6;         // pull workers per CTA (warps 6 .. 6 + kPullWarps - 1)
+constexpr int kPullChunk = 8;         // tickets drawn per atomic
 
 constexpr int MODE_PEER_WRITE = 0;
 constexpr int MODE_PULL = 1;
@@ -60,27 +62,40 @@ constexpr uint32_t ST_PULL_READY_TIMEOUT = 5;
 constexpr uint32_t ST_SMEM_MISALIGNED = 6;
 constexpr uint32_t ST_FLAG_TIMEOUT = 7;
 
+// Shared-memory plan. The N width of a tile (`tile_n`: 128, 192 or 256) and with
+// it the size and number of pipeline stages are chosen per problem on the
+// host, so the layout keeps a fixed 192 KiB stage area and room for the
+// largest stage count.
+constexpr int kMaxStages = 8;
+constexpr int kStageAreaBytes = 196608;
 template <int G>
 struct GemmCfg {
-  static constexpr int kStages = (G == 1) ? 4 : 6;
   static constexpr int kABytes = kBlockM * kBlockK * 2;         // 16 KB
-  static constexpr int kBRows = kBlockN / G;                    // W rows this CTA loads
-  static constexpr int kBBytes = kBRows * kBlockK * 2;          // 32 / 16 KB
-  static constexpr int kStageBytes = kABytes + kBBytes;         // 48 / 32 KB
-  static constexpr int kOffEpi = kStages * kStageBytes;         // 196608
+  static constexpr int kOffEpi = kStageAreaBytes;
   static constexpr int kOffBias = kOffEpi + 4 * kEpiBufs * kEpiBufBytes;
   static constexpr int kOffBar = kOffBias + 4 * kEpiCols * 4;
-  // full[kStages], empty[kStages], acc_full[2], acc_empty[2]
-  static constexpr int kNumBars = 2 * kStages + 2 * kAccStages;
+  // full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2]
+  static constexpr int kNumBars = 2 * kMaxStages + 2 * kAccStages;
   static constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
   static constexpr int kOffAbort = kOffTmemSlot + 4;
   static constexpr int kSmemBytes = kOffAbort + 4 + 56;         // small pad
   static constexpr int kUmmaM = kBlockM * G;
 };
 
+// W rows one CTA loads per stage, bytes of a stage, number of stages.
+__host__ __device__ constexpr int tile_b_rows(int tile_n, int g) { return tile_n / g; }
+__host__ __device__ constexpr int tile_stage_bytes(int tile_n, int g) {
+  return kBlockM * kBlockK * 2 + tile_b_rows(tile_n, g) * kBlockK * 2;
+}
+__host__ __device__ constexpr int tile_stages(int tile_n, int g) {
+  return kStageAreaBytes / tile_stage_bytes(tile_n, g) > kMaxStages
+             ? kMaxStages
+             : kStageAreaBytes / tile_stage_bytes(tile_n, g);
+}
+
 struct GemmParams {
   CUtensorMap map_a;                 // A  [M, K]   box 64 x 128
-  CUtensorMap map_b;                 // W  [N, K]   box 64 x (256/G)
+  CUtensorMap map_b;                 // W  [N, K]   box 64 x (tile_n/G)
   CUtensorMap map_out[kMaxPeers];    // peer-write: [rows, shard] slot in peer p; pull: [0] = out [M, N]
   const __nv_bfloat16* bias;         // nullptr when absent
   uint32_t* status;                  // error word (host-visible)
@@ -89,16 +104,19 @@ struct GemmParams {
   int shard;                         // exchanged columns per rank
   int up, rank;
   int n_rot;                         // peer-write: first N tile of this rank
-  int m_tiles, n_tiles, k_tiles;     // m_tiles counts (128*G)-row tiles
+  int m_tiles, n_tiles, k_tiles;     // m_tiles counts (128*G)-row tiles, n_tiles tile_n-column tiles
+  int tile_n;                        // 128, 192 or 256 output columns per tile
   // pull mode only
   const __nv_bfloat16* peers[kMaxPeers];  // staged arenas [up(dest), peer_rows, shard]
   __nv_bfloat16* dy;                 // dense pulled input [M, K]
   unsigned long long* ready;         // [ceil(M/128)] monotonically increasing ticket counts
-  unsigned long long* cursor;        // monotonically increasing ticket cursor
+  unsigned long long* cursor;        // monotonically increasing cursor, in chunks of kPullChunk tickets
   unsigned long long epoch1;         // launch ordinal, 1-based
-  unsigned long long cursor_base;    // cursor value that means "ticket 0" for this launch
+  unsigned long long cursor_base;    // cursor value that means "chunk 0" for this launch
   int peer_rows;
   int total_tickets;
+  int pull_stride;                   // pull warps in the grid: distance between the tickets of a chunk
+  int pull_rows;                     // rows per pull ticket: a power of two <= 16 with pull_rows * shard / 8 <= 512
   unsigned int flags;                // tuning switches (kFlag*)
   unsigned long long* trace;         // optional [grid][8] cycle counters (nullptr: off)
 };
@@ -112,9 +130,13 @@ constexpr int kTraceProdWait = 4;     // TMA producer waiting for a free stage (
 constexpr int kTraceEpiWait = 5;      // epilogue warp 2 waiting for a finished accumulator
 constexpr int kTraceNsStart = 6;      // %globaltimer at entry
 constexpr int kTraceNsEnd = 7;        // %globaltimer at exit
-constexpr int kTraceSlots = 8;
+constexpr int kTracePullEndNs = 8;    // %globaltimer when this CTA's pull workers ran out of tickets
+constexpr int kTracePullTickets = 9;  // tickets copied by this CTA's pull workers
+constexpr int kTraceGateFirstNs = 10; // ns from kernel entry until the producer's first panel gate opened
+constexpr int kTraceGateCycles = 11;  // producer cycles spent at panel gates
+constexpr int kTraceSlots = 16;
 
-constexpr unsigned int kFlagPairCommit = 1u;  // G=2: one commit to both CTAs instead of one per CTA
+constexpr unsigned int kFlagSplitCommit = 1u;  // G=2: one commit per CTA of the pair instead of one for both
 
 __device__ __forceinline__ void report_status(const GemmParams& p, volatile uint32_t* abort_flag,
                                               uint32_t code, uint32_t detail) {
@@ -124,8 +146,12 @@ __device__ __forceinline__ void report_status(const GemmParams& p, volatile uint
   }
 }
 
+__host__ __device__ constexpr int kernel_threads(int mode) {
+  return mode == MODE_PULL ? 192 + 32 * kPullWarps : 192;
+}
+
 template <int G, int MODE>
-__global__ void __launch_bounds__(MODE == MODE_PULL ? 256 : 192, 1)
+__global__ void __launch_bounds__(kernel_threads(MODE), 1)
 fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<G>;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -136,13 +162,16 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   const int cluster_id = blockIdx.x / G;
   const int num_clusters = gridDim.x / G;
   const int num_tiles = p.m_tiles * p.n_tiles;
+  const int tile_n = p.tile_n;
+  const int num_stages = tile_stages(tile_n, G);
+  const uint32_t stage_bytes = static_cast<uint32_t>(tile_stage_bytes(tile_n, G));
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_base = smem_base + Cfg::kOffBar;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
-  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + a); };
-  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + kAccStages + a); };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + kAccStages + a); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Cfg::kOffTmemSlot);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + Cfg::kOffAbort);
   const uint64_t timeout_ns = p.timeout_ns;
@@ -156,7 +185,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   if (threadIdx.x == 0) {
     *abort_flag = 0u;
     if ((smem_base & 1023u) != 0u) report_status(p, abort_flag, ST_SMEM_MISALIGNED, smem_base);
-    for (int s = 0; s < Cfg::kStages; ++s) {
+    for (int s = 0; s < num_stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -199,17 +228,18 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (n_blk >= p.n_tiles) n_blk -= p.n_tiles;
         const int panel = m_idx * G + static_cast<int>(cta_rank);
         const int a_row0 = panel * kBlockM;
-        const int b_row0 = n_blk * kBlockN + static_cast<int>(cta_rank) * Cfg::kBRows;
+        const int b_row0 = n_blk * tile_n + static_cast<int>(cta_rank) * tile_b_rows(tile_n, G);
         if constexpr (MODE == MODE_PULL) {
           // Gate on the pull workers having finished this 128-row panel.
-          const int groups_per_panel = kBlockM / kPullRowsPerTicket;
-          const int groups_total = (p.M + kPullRowsPerTicket - 1) / kPullRowsPerTicket;
+          const int groups_per_panel = kBlockM / p.pull_rows;
+          const int groups_total = (p.M + p.pull_rows - 1) / p.pull_rows;
           int groups = groups_total - panel * groups_per_panel;
           groups = groups < 0 ? 0 : (groups > groups_per_panel ? groups_per_panel : groups);
           const unsigned long long want =
               p.epoch1 * static_cast<unsigned long long>(groups) * static_cast<unsigned long long>(p.up);
           if (groups > 0) {
             const uint64_t t0 = globaltimer_ns();
+            const long long gate_c0 = trace ? clock64() : 0;
             uint32_t it = 0;
             while (ld_acquire_gpu_u64(reinterpret_cast<const uint64_t*>(p.ready + panel)) < want) {
               if ((++it & 0x3fu) == 0) {
@@ -222,6 +252,10 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
               }
             }
             if (!ok) break;
+            if (trace) {
+              trace[kTraceGateCycles] += static_cast<unsigned long long>(clock64() - gate_c0);
+              if (trace[kTraceGateFirstNs] == 0) trace[kTraceGateFirstNs] = globaltimer_ns() - trace[kTraceNsStart];
+            }
             fence_proxy_async_all();  // generic-proxy writes of dy -> async-proxy (TMA) reads
           }
         }
@@ -234,22 +268,22 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
             ok = false;
             break;
           }
-          const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
+          const uint32_t a_dst = smem_base + stage * stage_bytes;
           const uint32_t b_dst = a_dst + Cfg::kABytes;
           if constexpr (G == 1) {
-            mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes);
+            mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
             tma_load_2d(a_dst, &p.map_a, kt * kBlockK, a_row0, full_bar(stage));
             tma_load_2d(b_dst, &p.map_b, kt * kBlockK, b_row0, full_bar(stage));
           } else {
             // Both CTAs' loads complete on the leader's barrier, which the
             // leader arms for the bytes of the whole pair.
             const uint32_t bar = leader_full0 + 8u * stage;
-            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * Cfg::kStageBytes);
+            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * stage_bytes);
             tma_load_2d_pair(a_dst, &p.map_a, kt * kBlockK, a_row0, bar);
             tma_load_2d_pair(b_dst, &p.map_b, kt * kBlockK, b_row0, bar);
           }
-          if (in_flight < static_cast<uint32_t>(Cfg::kStages)) ++in_flight;
-          if (++stage == Cfg::kStages) {
+          if (in_flight < static_cast<uint32_t>(num_stages)) ++in_flight;
+          if (++stage == static_cast<uint32_t>(num_stages)) {
             stage = 0;
             phase ^= 1u;
           }
@@ -262,7 +296,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         uint32_t s = stage, ph = phase;
         for (uint32_t i = 0; i < in_flight; ++i) {
           if (s == 0) {
-            s = Cfg::kStages;
+            s = static_cast<uint32_t>(num_stages);
             ph ^= 1u;
           }
           --s;
@@ -275,75 +309,80 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   }
 
   // --------------------------------------------------------------- MMA issue
+  // The whole warp runs this loop in lock-step and one elected lane issues the
+  // tcgen05 instructions: with warp-uniform control flow the descriptors stay
+  // in uniform registers and an iteration costs ~50 cycles on top of the four
+  // 128-cycle MMAs; a loop run by a single lane inside a divergent branch
+  // measured ~250 cycles of overhead per K step and starved the tensor pipe.
   if (warp == 1 && !misaligned && cta_rank == 0) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(Cfg::kUmmaM, kBlockN);
-      uint32_t stage = 0, phase = 0;
-      uint32_t acc_it = 0;
-      bool ok = true;
-      long long wait_full = 0, wait_acc = 0;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++acc_it) {
-        const uint32_t as = acc_it & 1u;
-        const uint32_t aphase = (acc_it >> 1) & 1u;
-        const long long t_acc = trace ? clock64() : 0;
-        const bool acc_free = mbar_wait_bounded(acc_empty_bar(as), aphase ^ 1u, abort_flag, timeout_ns);
-        if (trace) wait_acc += clock64() - t_acc;
-        if (!acc_free) {
-          report_status(p, abort_flag, ST_MMA_ACC_TIMEOUT, static_cast<uint32_t>(tile));
-          ok = false;
-          break;
+    const uint32_t idesc = make_idesc_bf16(Cfg::kUmmaM, tile_n);
+    const uint64_t desc0 = make_kmajor_sw128_desc(smem_base);
+    const uint64_t desc_step = static_cast<uint64_t>(stage_bytes >> 4);
+    const bool pair_commit = (G == 2) && (p.flags & kFlagSplitCommit) == 0u;
+    uint32_t stage = 0, phase = 0;
+    uint32_t acc_it = 0;
+    bool failed = false;
+    long long wait_full = 0, wait_acc = 0;
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++acc_it) {
+      const uint32_t as = acc_it & 1u;
+      const uint32_t aphase = (acc_it >> 1) & 1u;
+      const long long t_acc = trace ? clock64() : 0;
+      if (!mbar_wait_bounded(acc_empty_bar(as), aphase ^ 1u, abort_flag, timeout_ns)) {
+        report_status(p, abort_flag, ST_MMA_ACC_TIMEOUT, static_cast<uint32_t>(tile));
+        failed = true;
+      }
+      if (trace) wait_acc += clock64() - t_acc;
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + as * kBlockN;
+      for (int kt = 0; kt < p.k_tiles; ++kt) {
+        const long long t_full = trace ? clock64() : 0;
+        if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, timeout_ns)) {
+          report_status(p, abort_flag, ST_MMA_FULL_TIMEOUT, static_cast<uint32_t>(tile));
+          failed = true;
         }
+        if (trace) wait_full += clock64() - t_full;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + as * kBlockN;
-        for (int kt = 0; kt < p.k_tiles; ++kt) {
-          const long long t_full = trace ? clock64() : 0;
-          const bool filled = mbar_wait_bounded(full_bar(stage), phase, abort_flag, timeout_ns);
-          if (trace) wait_full += clock64() - t_full;
-          if (!filled) {
-            report_status(p, abort_flag, ST_MMA_FULL_TIMEOUT, static_cast<uint32_t>(tile));
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_base + stage * Cfg::kStageBytes;
-          const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
-          const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + Cfg::kABytes);
-#pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            // 16 BF16 = 32 bytes further along K inside the 128-byte swizzle row
-            const uint64_t koff = static_cast<uint64_t>((k * kUmmaK * 2) >> 4);
-            umma_bf16<G>(d_tmem, a_desc + koff, b_desc + koff, idesc,
-                         (kt > 0 || k > 0) ? 1u : 0u);
-          }
+        const uint64_t a_desc = desc0 + desc_step * stage;
+        const uint64_t b_desc = a_desc + static_cast<uint64_t>(Cfg::kABytes >> 4);
+        if (elect_one_sync()) {
+          // 16 BF16 = 32 bytes further along K inside the 128-byte swizzle row per step
+          umma_bf16<G>(d_tmem, a_desc, b_desc, idesc, kt > 0 ? 1u : 0u);
+          umma_bf16<G>(d_tmem, a_desc + 2, b_desc + 2, idesc, 1u);
+          umma_bf16<G>(d_tmem, a_desc + 4, b_desc + 4, idesc, 1u);
+          umma_bf16<G>(d_tmem, a_desc + 6, b_desc + 6, idesc, 1u);
           // Release the shared-memory slot once these MMAs have read it.
           if constexpr (G == 1) {
             umma_commit_1(empty_bar(stage));
-          } else if (p.flags & kFlagPairCommit) {
+          } else if (pair_commit) {
             umma_commit_2_mask(empty_bar(stage), 3);
           } else {
             umma_commit_2(mapa_cluster(empty_bar(stage), 0));
             umma_commit_2(mapa_cluster(empty_bar(stage), 1));
           }
-          if (++stage == Cfg::kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
         }
-        if (!ok) break;
-        // Publish the finished accumulator to the epilogue warps.
+        if (++stage == static_cast<uint32_t>(num_stages)) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      // Publish the finished accumulator to the epilogue warps.
+      if (elect_one_sync()) {
         if constexpr (G == 1) {
           umma_commit_1(acc_full_bar(as));
-        } else if (p.flags & kFlagPairCommit) {
+        } else if (pair_commit) {
           umma_commit_2_mask(acc_full_bar(as), 3);
         } else {
           umma_commit_2(mapa_cluster(acc_full_bar(as), 0));
           umma_commit_2(mapa_cluster(acc_full_bar(as), 1));
         }
       }
-      if (trace) {
-        trace[kTraceMmaWaitFull] = static_cast<unsigned long long>(wait_full);
-        trace[kTraceMmaWaitAcc] = static_cast<unsigned long long>(wait_acc);
-      }
+      // A lane whose wait ran out has raised the abort flag, which makes every
+      // later wait return at once; the warp leaves together at a tile boundary.
+      if (__any_sync(0xffffffffu, failed)) break;
+    }
+    if (trace && lane == 0) {
+      trace[kTraceMmaWaitFull] = static_cast<unsigned long long>(wait_full);
+      trace[kTraceMmaWaitAcc] = static_cast<unsigned long long>(wait_acc);
     }
   }
 
@@ -378,10 +417,12 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       tc_fence_after_sync();
 
 #pragma unroll 1
-      for (int c = 0; c < kBlockN / kEpiCols; ++c) {
-        const int gcol = n_blk * kBlockN + c * kEpiCols;
+      const int chunks = tile_n / kEpiCols;
+      for (int c = 0; c < chunks; ++c) {
+        const int gcol = n_blk * tile_n + c * kEpiCols;
+        const bool in_range = gcol < p.N;  // the last tile of a row may hang over N
         // Bias for these 64 columns, widened to FP32, shared inside the warp.
-        if (p.bias != nullptr) {
+        if (p.bias != nullptr && in_range) {
           const __nv_bfloat162 b2 =
               *reinterpret_cast<const __nv_bfloat162*>(p.bias + gcol + 2 * lane);
           bias_s[2 * lane] = __bfloat162float(b2.x);
@@ -393,7 +434,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         tmem_ld_32x32(taddr, v[0]);
         tmem_ld_32x32(taddr + 32, v[1]);
         tmem_ld_wait();
-        if (c == kBlockN / kEpiCols - 1) {
+        if (c == chunks - 1) {
           // Accumulator fully read: hand the TMEM stage back to the MMA warp.
           tc_fence_before_sync();
           __syncwarp();
@@ -439,7 +480,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (row0 < p.M) {
+          if (row0 < p.M && in_range) {
             if constexpr (MODE == MODE_PEER_WRITE) {
               const int dst = gcol / p.shard;
               const int lcol = gcol - dst * p.shard;
@@ -462,54 +503,95 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   }
 
   // ------------------------------------------------------------ pull workers
+  // A ticket is one batch: up to 512 sixteen-byte vectors (pull_rows rows of one
+  // peer shard), all loaded before the first is stored, so it costs one round
+  // trip over NVLink. Tickets are numbered in the order the GEMM consumes
+  // panels. One atomic draws a chunk of kPullChunk tickets (same-address atomics
+  // serialise at ~8 ns each across the GPU, so one draw per ticket would be the
+  // bottleneck); the chunk's tickets are `pull_stride` apart (the number of pull
+  // warps in the grid), so that in their i-th round trip all warps together copy
+  // the i-th run of consecutive tickets and panels complete in consumption
+  // order. A ticket is published (proxy fence + release) while the next
+  // ticket's loads are in flight.
   if constexpr (MODE == MODE_PULL) {
     if (warp >= 6 && !misaligned) {
       const int vec_per_row = p.shard >> 3;  // 16-byte vectors per shard row
+      const int groups_per_panel = kBlockM / p.pull_rows;
       const unsigned long long total = static_cast<unsigned long long>(p.total_tickets);
-      for (;;) {
-        unsigned long long t = 0;
-        if (lane == 0) t = atomicAdd(p.cursor, 1ull) - p.cursor_base;
-        t = __shfl_sync(0xffffffffu, t, 0);
-        if (t >= total || *abort_flag != 0u) break;
-        const int grp = static_cast<int>(t / static_cast<unsigned long long>(p.up));
-        int src_rank = static_cast<int>(t - static_cast<unsigned long long>(grp) * p.up) + p.rank + 1;
-        if (src_rank >= p.up) src_rank -= p.up;
-        const int r0 = grp * kPullRowsPerTicket;
-        int nrows = p.M - r0;
-        nrows = nrows > kPullRowsPerTicket ? kPullRowsPerTicket : nrows;
-        const int nvec = nrows * vec_per_row;
-        const __nv_bfloat16* src =
-            p.peers[src_rank] +
-            (static_cast<size_t>(p.rank) * p.peer_rows + r0) * static_cast<size_t>(p.shard);
-        __nv_bfloat16* dst = p.dy + static_cast<size_t>(r0) * p.K +
-                             static_cast<size_t>(src_rank) * p.shard;
-        for (int base = 0; base < nvec; base += 32 * kPullUnroll) {
-          uint4 regs[kPullUnroll];
-          int rr[kPullUnroll], cc[kPullUnroll];
-#pragma unroll
-          for (int u = 0; u < kPullUnroll; ++u) {
-            const int vidx = base + u * 32 + lane;
-            rr[u] = vidx / vec_per_row;
-            cc[u] = vidx - rr[u] * vec_per_row;
-            if (vidx < nvec) {
-              regs[u] = ld_stream_v4(src + static_cast<size_t>(rr[u]) * p.shard + cc[u] * 8);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < kPullUnroll; ++u) {
-            const int vidx = base + u * 32 + lane;
-            if (vidx < nvec) {
-              *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rr[u]) * p.K + cc[u] * 8) = regs[u];
-            }
-          }
-        }
-        __syncwarp();
+      const unsigned long long stride = static_cast<unsigned long long>(p.pull_stride);
+      const unsigned long long block = stride * kPullChunk;  // tickets covered by `stride` chunks
+      const unsigned long long chunks = (total + block - 1) / block * stride;
+      auto draw = [&]() -> unsigned long long {
+        unsigned long long c = 0;
+        if (lane == 0) c = atomicAdd(p.cursor, 1ull) - p.cursor_base + stride;
+        return __shfl_sync(0xffffffffu, c, 0);
+      };
+      auto publish = [&](int panel) {
+        // every lane's stores of that ticket precede this point (__syncwarp below)
         if (lane == 0) {
-          fence_proxy_async_all();
-          __threadfence();
-          red_release_gpu_add_u64(reinterpret_cast<uint64_t*>(p.ready + grp / (kBlockM / kPullRowsPerTicket)),
-                                  1ull);
+          fence_proxy_async_global();  // generic-proxy stores before the consumers' TMA (async-proxy) loads
+          fence_acq_rel_gpu();
+          red_release_gpu_add_u64(reinterpret_cast<uint64_t*>(p.ready + panel), 1ull);
         }
+      };
+      int pending_panel = -1;
+      int tickets_done = 0;
+      // The first chunk of every pull warp is its own index (no atomic on the
+      // critical path of the first panels); the cursor hands out the rest.
+      unsigned long long c = static_cast<unsigned long long>(blockIdx.x) * kPullWarps + (warp - 6);
+      while (c < chunks && *abort_flag == 0u) {
+        const unsigned long long c_next = draw();
+        const unsigned long long t_first = (c / stride) * block + (c % stride);
+        for (int i = 0; i < kPullChunk; ++i) {
+          const unsigned long long t = t_first + static_cast<unsigned long long>(i) * stride;
+          if (t >= total) break;
+          const int grp = static_cast<int>(t / static_cast<unsigned long long>(p.up));
+          int src_rank = static_cast<int>(t - static_cast<unsigned long long>(grp) * p.up) + p.rank + 1;
+          if (src_rank >= p.up) src_rank -= p.up;
+          const int r0 = grp * p.pull_rows;
+          int nrows = p.M - r0;
+          nrows = nrows > p.pull_rows ? p.pull_rows : nrows;
+          const int nvec = nrows * vec_per_row;  // <= kPullMaxVecs
+          const __nv_bfloat16* src =
+              p.peers[src_rank] +
+              (static_cast<size_t>(p.rank) * p.peer_rows + r0) * static_cast<size_t>(p.shard);
+          __nv_bfloat16* dst = p.dy + static_cast<size_t>(r0) * p.K +
+                               static_cast<size_t>(src_rank) * p.shard;
+          uint4 regs[kPullUnroll];
+#pragma unroll
+          for (int u = 0; u < kPullUnroll; ++u) {
+            const int vidx = u * 32 + lane;
+            if (vidx < nvec) {
+              const int rr = vidx / vec_per_row;
+              const int cc = vidx - rr * vec_per_row;
+              regs[u] = ld_stream_v4(src + static_cast<size_t>(rr) * p.shard + cc * 8);
+            }
+          }
+          if (pending_panel >= 0) publish(pending_panel);
+#pragma unroll
+          for (int u = 0; u < kPullUnroll; ++u) {
+            const int vidx = u * 32 + lane;
+            if (vidx < nvec) {
+              const int rr = vidx / vec_per_row;
+              const int cc = vidx - rr * vec_per_row;
+              *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rr) * p.K + cc * 8) = regs[u];
+            }
+          }
+          __syncwarp();
+          pending_panel = grp / groups_per_panel;
+          if (tickets_done < 2) {
+            // start-up: the first panels gate every CTA, publish them at once
+            publish(pending_panel);
+            pending_panel = -1;
+          }
+          ++tickets_done;
+        }
+        c = c_next;
+      }
+      if (pending_panel >= 0) publish(pending_panel);
+      if (trace && lane == 0) {
+        atomicMax(trace + kTracePullEndNs, static_cast<unsigned long long>(globaltimer_ns()));
+        atomicAdd(trace + kTracePullTickets, static_cast<unsigned long long>(tickets_done));
       }
     }
   }

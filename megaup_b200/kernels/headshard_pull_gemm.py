@@ -46,13 +46,13 @@ class CompiledHeadShardPullGemm:
         self.logical_m = rows
         self.rank = rank
         self.up = up
-        self.tile_n = TILE_N
-        grid, group, smem = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        grid, group, smem, tile = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
         launches = ctypes.c_uint64()
         _native.call(
             "mup_pull_plan_info", plan, ctypes.byref(grid), ctypes.byref(group),
-            ctypes.byref(launches), ctypes.byref(smem),
+            ctypes.byref(launches), ctypes.byref(smem), ctypes.byref(tile),
         )
+        self.tile_n = tile.value
         self.grid_ctas = grid.value
         self.cta_group = group.value
         self.smem_bytes = smem.value

@@ -72,11 +72,12 @@ class PeerWriteLaunch:
         self.rows = rows
         self.local_rank = local_rank
         self.out_features, self.in_features = map(int, weight.shape)
-        grid, group, rotation, smem = (ctypes.c_int() for _ in range(4))
+        grid, group, rotation, smem, tile = (ctypes.c_int() for _ in range(5))
         _native.call(
             "mup_peer_write_plan_info", plan, ctypes.byref(grid), ctypes.byref(group),
-            ctypes.byref(rotation), ctypes.byref(smem),
+            ctypes.byref(rotation), ctypes.byref(smem), ctypes.byref(tile),
         )
+        self.tile_n = tile.value
         self.grid_ctas = grid.value
         self.cta_group = group.value
         self.n_rotation = rotation.value

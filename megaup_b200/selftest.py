@@ -54,7 +54,7 @@ def main() -> int:
     stream = torch.cuda.current_stream(device).cuda_stream
     timeout_ns = 2_000_000_000
     plan = ctypes.c_void_p()
-    grid, group, smem = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    grid, group, smem, tile = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
     report: dict[str, object] = {
         "mode": args.mode, "rows": rows, "n": n, "k": k, "up": up, "rank": rank, "bias": bias is not None,
     }
@@ -71,7 +71,7 @@ def main() -> int:
         rotation = ctypes.c_int()
         _native.call(
             "mup_peer_write_plan_info", plan, ctypes.byref(grid), ctypes.byref(group),
-            ctypes.byref(rotation), ctypes.byref(smem),
+            ctypes.byref(rotation), ctypes.byref(smem), ctypes.byref(tile),
         )
 
         def launch() -> None:
@@ -98,7 +98,7 @@ def main() -> int:
         launches = ctypes.c_uint64()
         _native.call(
             "mup_pull_plan_info", plan, ctypes.byref(grid), ctypes.byref(group),
-            ctypes.byref(launches), ctypes.byref(smem),
+            ctypes.byref(launches), ctypes.byref(smem), ctypes.byref(tile),
         )
 
         def launch() -> None:
@@ -113,7 +113,7 @@ def main() -> int:
 
     status = int(host_status[0])
     report.update(
-        grid_ctas=grid.value, cta_group=group.value, smem_bytes=smem.value, status=status,
+        grid_ctas=grid.value, cta_group=group.value, tile_n=tile.value, smem_bytes=smem.value, status=status,
         status_text=_native.decode_status(status),
         bitwise_vs_cublas=bool(torch.equal(got, want)),
         mismatches=int((got != want).sum()),
@@ -121,7 +121,7 @@ def main() -> int:
     )
     trace = None
     if args.trace:
-        trace = torch.zeros((grid.value, 8), dtype=torch.int64, device=device)
+        trace = torch.zeros((grid.value, 16), dtype=torch.int64, device=device)
         setter = "mup_peer_write_plan_set_trace" if args.mode == "peer_write" else "mup_pull_plan_set_trace"
         _native.call(setter, plan, trace.data_ptr())
     if args.iters and status == 0:
@@ -139,6 +139,7 @@ def main() -> int:
         report["tflops"] = 2.0 * rows * n * k / us / 1e6
         report["status_after_timing"] = int(host_status[0])
     if trace is not None:
+        trace.zero_()
         launch()
         torch.cuda.synchronize(device)
         t = trace.cpu().double()
@@ -154,6 +155,12 @@ def main() -> int:
             "producer_wait_stage_mean": float(t[:, 4].mean()),
             "epilogue_wait_mean": float(t[:, 5].mean()),
         }
+        if args.mode == "pull":
+            report["trace"]["pull_done_us_after_start"] = float(t[:, 8].max() - t[:, 6].min()) / 1e3
+            report["trace"]["pull_tickets_min_max"] = [float(t[:, 9].min()), float(t[:, 9].max())]
+            gate = t[:, 10] / 1e3
+            report["trace"]["first_gate_open_us_min_mean_max"] = [float(gate.min()), float(gate.mean()), float(gate.max())]
+            report["trace"]["gate_cycles_mean"] = float(t[:, 11].mean())
     print("[SELFTEST] " + json.dumps(report), flush=True)
     ok = status == 0 and report["exchange_exact"] and (report["bitwise_vs_cublas"] or rows < 256)
     return 0 if ok else 1
