@@ -35,10 +35,9 @@ if str(ROOT) not in sys.path:
 HIDDEN, HEADS, HEAD_DIM, TOKENS = 5120, 40, 128, 4096
 FLOPS_PER_CALL = 2.0 * TOKENS * HIDDEN * HIDDEN
 NVLINK_BYTES_PER_S = 900e9
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the peer-write
-# kernel at this shape, from the ncu capture summarised under profiles/
-# (None until a capture has been taken).
-PEER_WRITE_DRAM_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the two GEMM kernels
+# at this shape, from the ncu captures summarised under profiles/ (UP=8, one GPU).
+DRAM_TRAFFIC_BYTES = {"peer_write": 205.6e6 + 32.6e6, "head_shard_pull": 201.0e6 + 73.0e6}
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -499,7 +498,8 @@ def main() -> None:
                 "peak": burst,
                 "unit": "TFLOP/s",
                 "frac": FLOPS_PER_CALL / dominant_us / 1e6 / burst,
-                "traffic": PEER_WRITE_DRAM_TRAFFIC_BYTES,
+                "traffic": DRAM_TRAFFIC_BYTES[dominant],
+                "traffic_source": "ncu capture of this kernel at this shape with UP=8 emulated on one GPU (profiles/)",
                 "peak_source": f"{peak_kind} burst bf16 (MEASURED_PEAKS.json)" if peak_kind == "measured" else "fallback",
                 "flops_per_launch": FLOPS_PER_CALL,
                 "us_per_launch": dominant_us,
