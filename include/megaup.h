@@ -107,6 +107,32 @@ int mup_arena_destroy(mup_arena *arena);
 int mup_flag_barrier(void *const *peer_flags, int up, int rank, uint32_t epoch,
                      void *status_device_ptr, uint64_t timeout_ns, void *stream);
 
+/* ---- hand-off folded into the kernels ----------------------------------------- */
+
+/* Sync points form one sequence that every rank walks through in the same
+ * order (a stand-alone mup_flag_barrier is "signal e, then wait e"). The
+ * *_synced launches below fold the two halves into the kernels around them:
+ * the kernel waits for `wait_epoch` before it first touches memory the
+ * hand-off protects (0: no wait) and, once all of its CTAs have finished the
+ * work `signal_epoch` stands for, raises that epoch at every peer (0: no
+ * signal). This replaces the two barrier kernels per operation of the
+ * reference's protocol (mega_up/runtime.py:264, :281, :415, :421).
+ * `done_counter` is a zero-initialised device uint64 that only ever grows;
+ * pass its expected value before the launch in `done_before` and read the
+ * value it will have afterwards from `done_after`. */
+typedef struct mup_sync {
+  void *const *peer_flags; /* [up] flag arrays as in mup_flag_barrier */
+  int up;
+  int rank;
+  uint32_t wait_epoch;
+  uint32_t signal_epoch;
+  void *done_counter;
+  uint64_t done_before;
+  uint64_t done_after; /* out */
+  void *status_device_ptr;
+  uint64_t timeout_ns;
+} mup_sync;
+
 /* ---- peer-write GEMM ------------------------------------------------------- */
 
 /* Bind out = bf16(A[rows,k] @ W[n,k]^T + bias) whose column block p lands in
@@ -121,6 +147,12 @@ int mup_peer_write_plan_create(mup_peer_write_plan **out, int device, int rows, 
 /* Launch on `stream` for input `a` ([rows, k] BF16, 16-byte aligned).
  * Replaces PeerWriteLaunch.__call__ (peer_write_gemm.py:2677-2694). */
 int mup_peer_write_launch(mup_peer_write_plan *plan, const void *a, void *stream);
+/* As mup_peer_write_launch; the first store into a peer slot waits for
+ * sync->wait_epoch (the owners have copied the previous result out) and the
+ * last CTA to finish its stores signals sync->signal_epoch. sync == NULL
+ * behaves like mup_peer_write_launch. */
+int mup_peer_write_launch_synced(mup_peer_write_plan *plan, const void *a, void *stream,
+                                 mup_sync *sync);
 /* Any output pointer may be NULL. tile_n is the width of an output tile the
  * library chose for this problem (128, 192 or 256 columns). */
 int mup_peer_write_plan_info(const mup_peer_write_plan *plan, int *grid_ctas, int *cta_group,
@@ -152,6 +184,11 @@ int mup_pull_plan_create(mup_pull_plan **out, int device, int rows, int n, int k
                          int cta_group, void *status_device_ptr, uint64_t timeout_ns);
 /* Replaces CompiledHeadShardPullGemm.__call__ (headshard_pull_gemm.py:2407-2428). */
 int mup_pull_launch(mup_pull_plan *plan, void *stream);
+/* As mup_pull_launch; the pull workers wait for sync->wait_epoch (the peers
+ * have staged their shards) before their first peer load, and the last pull
+ * warp to run out of tickets signals sync->signal_epoch (this rank will not
+ * read a peer arena again), typically long before the GEMM itself ends. */
+int mup_pull_launch_synced(mup_pull_plan *plan, void *stream, mup_sync *sync);
 /* After a device-side failure the counters are inconsistent: zero the
  * workspace on `stream` and restart the launch ordinal. Replaces
  * CompiledHeadShardPullGemm.reset_workspace (headshard_pull_gemm.py:2393-2405). */
@@ -206,12 +243,22 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
 int mup_gather_rows(void *dst, const void *src, const int64_t *index, int64_t rows,
                     int64_t row_elems, void *stream);
 
+/* mup_gather_rows with the hand-off folded in: every block waits for
+ * sync->wait_epoch before it reads or writes, the last block to finish
+ * signals sync->signal_epoch. */
+int mup_gather_rows_synced(void *dst, const void *src, const int64_t *index, int64_t rows,
+                           int64_t row_elems, void *stream, mup_sync *sync);
+
 /* Batched source-major <-> batch-major regroup of dense rows:
  * dst[(b*up + r)*seq + s] = src[(r*batch + b)*seq + s]   when to_batch_major,
  * dst[(r*batch + b)*seq + s] = src[(b*up + r)*seq + s]   otherwise.
  * Replaces the permuted copy_ at mega_up/runtime.py:272-280 and :399-414. */
 int mup_regroup_rows(void *dst, const void *src, int up, int batch, int64_t seq,
                      int64_t row_elems, int to_batch_major, void *stream);
+
+/* mup_regroup_rows with the hand-off folded in (see mup_gather_rows_synced). */
+int mup_regroup_rows_synced(void *dst, const void *src, int up, int batch, int64_t seq,
+                            int64_t row_elems, int to_batch_major, void *stream, mup_sync *sync);
 
 #ifdef __cplusplus
 }

@@ -31,6 +31,23 @@ STATUS_NAMES = {
     7: "slot hand-off flag was not raised by a peer in time",
 }
 
+class MupSync(ctypes.Structure):
+    """``mup_sync`` of include/megaup.h: a hand-off folded into a launch."""
+
+    _fields_ = [
+        ("peer_flags", POINTER(c_void_p)),
+        ("up", c_int),
+        ("rank", c_int),
+        ("wait_epoch", c_uint32),
+        ("signal_epoch", c_uint32),
+        ("done_counter", c_void_p),
+        ("done_before", c_uint64),
+        ("done_after", c_uint64),
+        ("status_device_ptr", c_void_p),
+        ("timeout_ns", c_uint64),
+    ]
+
+
 # name -> (restype, argtypes); must list every symbol include/megaup.h declares.
 SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
     "mup_abi_version": (c_int, ()),
@@ -56,6 +73,7 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
         ),
     ),
     "mup_peer_write_launch": (c_int, (c_void_p, c_void_p, c_void_p)),
+    "mup_peer_write_launch_synced": (c_int, (c_void_p, c_void_p, c_void_p, POINTER(MupSync))),
     "mup_peer_write_plan_info": (
         c_int,
         (c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)),
@@ -72,6 +90,7 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
         ),
     ),
     "mup_pull_launch": (c_int, (c_void_p, c_void_p)),
+    "mup_pull_launch_synced": (c_int, (c_void_p, c_void_p, POINTER(MupSync))),
     "mup_pull_plan_reset": (c_int, (c_void_p, c_void_p)),
     "mup_pull_plan_info": (
         c_int,
@@ -87,6 +106,14 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
         ),
     ),
     "mup_gather_rows": (c_int, (c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p)),
+    "mup_gather_rows_synced": (
+        c_int,
+        (c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, POINTER(MupSync)),
+    ),
+    "mup_regroup_rows_synced": (
+        c_int,
+        (c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p, POINTER(MupSync)),
+    ),
     "mup_regroup_rows": (
         c_int,
         (c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p),

@@ -161,6 +161,33 @@ int n_rotation(int rank, int up, int n_total, int tile_n) {
   return ((rank * n_tiles + up - 1) / up) % n_tiles;
 }
 
+// Translate the C-ABI hand-off description; `participants` = arrivals this launch adds to the counter.
+int fill_sync(mup::SyncParams* sp, mup_sync* sync, unsigned long long participants) {
+  memset(sp, 0, sizeof(*sp));
+  if (sync == nullptr) return MUP_OK;
+  if (sync->peer_flags == nullptr || sync->up < 1 || sync->up > mup::kMaxPeers || sync->rank < 0 ||
+      sync->rank >= sync->up)
+    return fail(MUP_ERR_BAD_ARG, "bad hand-off description (flags, up or rank)");
+  if (sync->signal_epoch != 0 && sync->done_counter == nullptr)
+    return fail(MUP_ERR_BAD_ARG, "a hand-off that signals needs a done counter");
+  if (reinterpret_cast<uintptr_t>(sync->done_counter) % 8)
+    return fail(MUP_ERR_BAD_ARG, "done counter must be 8-byte aligned");
+  for (int i = 0; i < sync->up; ++i) {
+    if (sync->peer_flags[i] == nullptr) return fail(MUP_ERR_BAD_ARG, "flag array %d is null", i);
+    sp->flags[i] = static_cast<uint32_t*>(sync->peer_flags[i]);
+  }
+  sp->done = static_cast<unsigned long long*>(sync->done_counter);
+  sp->done_target = sync->done_before + participants;
+  sp->status = static_cast<uint32_t*>(sync->status_device_ptr);
+  sp->timeout_ns = sync->timeout_ns;
+  sp->wait_epoch = sync->wait_epoch;
+  sp->signal_epoch = sync->signal_epoch;
+  sp->up = sync->up;
+  sp->rank = sync->rank;
+  sync->done_after = (sync->signal_epoch != 0) ? sp->done_target : sync->done_before;
+  return MUP_OK;
+}
+
 struct DeviceInfo {
   int sms = 0;
   int cc_major = 0;
@@ -422,6 +449,72 @@ __global__ void regroup_rows_kernel(uint4* __restrict__ dst, const uint4* __rest
     }
     dst[i] = src[srow * vecs + col];
   }
+}
+
+// The two copies with the hand-off folded in: every block waits (thread 0
+// polls this rank's flags) before it touches the slots, and counts itself in
+// after its last store; the last block raises the flags at the peers.
+__global__ void gather_rows_synced_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                          const int64_t* __restrict__ index, int64_t rows,
+                                          int64_t vecs, mup::SyncParams sp) {
+  // threads 0 .. up-1 poll one peer's flag each; the block proceeds on a unanimous vote
+  const int handed = __syncthreads_and(mup::sync_wait_one(sp, static_cast<int>(threadIdx.x)) ? 1 : 0);
+  if (handed) {
+    const int64_t total = rows * vecs;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += stride) {
+      const int64_t row = i / vecs;
+      const int64_t col = i - row * vecs;
+      const int64_t srow = (index != nullptr) ? index[row] : row;
+      dst[i] = src[srow * vecs + col];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mup::sync_arrive_and_signal(sp);
+}
+
+__global__ void regroup_rows_synced_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                           int up, int batch, int64_t seq, int64_t vecs,
+                                           int to_batch_major, mup::SyncParams sp) {
+  // threads 0 .. up-1 poll one peer's flag each; the block proceeds on a unanimous vote
+  const int handed = __syncthreads_and(mup::sync_wait_one(sp, static_cast<int>(threadIdx.x)) ? 1 : 0);
+  if (handed) {
+    const int64_t rows = static_cast<int64_t>(up) * batch * seq;
+    const int64_t total = rows * vecs;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += stride) {
+      const int64_t row = i / vecs;
+      const int64_t col = i - row * vecs;
+      const int64_t s = row % seq;
+      const int64_t outer = row / seq;
+      int64_t srow;
+      if (to_batch_major) {
+        const int64_t r = outer % up;
+        const int64_t b = outer / up;
+        srow = (r * batch + b) * seq + s;
+      } else {
+        const int64_t b = outer % batch;
+        const int64_t r = outer / batch;
+        srow = (b * up + r) * seq + s;
+      }
+      dst[i] = src[srow * vecs + col];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mup::sync_arrive_and_signal(sp);
+}
+
+// Grid of a copy that carries a hand-off: at most the blocks that are resident
+// at once (8 x 256 threads per SM), so that every block's wait is paid once,
+// concurrently, and the arrival counter sees few atomics.
+int synced_copy_grid(int64_t total_vecs) {
+  int64_t blocks = (total_vecs + 255) / 256;
+  const int64_t cap = 148 * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks);
 }
 
 int copy_grid(int64_t total_vecs) {
@@ -695,6 +788,16 @@ int mup_peer_write_launch(mup_peer_write_plan* plan, const void* a, void* stream
   return launch_kernel<1, mup::MODE_PEER_WRITE>(p, plan->core.grid, s);
 }
 
+int mup_peer_write_launch_synced(mup_peer_write_plan* plan, const void* a, void* stream,
+                                 mup_sync* sync) {
+  if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
+  int rc = fill_sync(&plan->core.params.sync, sync, static_cast<unsigned long long>(plan->core.grid));
+  if (rc != MUP_OK) return rc;
+  rc = mup_peer_write_launch(plan, a, stream);
+  memset(&plan->core.params.sync, 0, sizeof(plan->core.params.sync));
+  return rc;
+}
+
 int mup_peer_write_plan_info(const mup_peer_write_plan* plan, int* grid_ctas, int* cta_group,
                              int* n_rotation_out, int* smem_bytes, int* tile_n) {
   if (plan != nullptr && tile_n != nullptr) *tile_n = plan->core.params.tile_n;
@@ -801,6 +904,15 @@ int mup_pull_launch(mup_pull_plan* plan, void* stream) {
   int rc = (plan->core.cta_group == 2) ? launch_kernel<2, mup::MODE_PULL>(p, plan->core.grid, s)
                                        : launch_kernel<1, mup::MODE_PULL>(p, plan->core.grid, s);
   if (rc == MUP_OK) plan->launches += 1;
+  return rc;
+}
+
+int mup_pull_launch_synced(mup_pull_plan* plan, void* stream, mup_sync* sync) {
+  if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
+  int rc = fill_sync(&plan->core.params.sync, sync, plan->pull_warps);
+  if (rc != MUP_OK) return rc;
+  rc = mup_pull_launch(plan, stream);
+  memset(&plan->core.params.sync, 0, sizeof(plan->core.params.sync));
   return rc;
 }
 
@@ -1008,6 +1120,43 @@ int mup_gather_rows(void* dst, const void* src, const int64_t* index, int64_t ro
   const int64_t vecs = row_elems / 8;
   gather_rows_kernel<<<copy_grid(rows * vecs), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<uint4*>(dst), static_cast<const uint4*>(src), index, rows, vecs);
+  MUP_CUDA(cudaGetLastError());
+  return MUP_OK;
+}
+
+int mup_gather_rows_synced(void* dst, const void* src, const int64_t* index, int64_t rows,
+                           int64_t row_elems, void* stream, mup_sync* sync) {
+  if (dst == nullptr || src == nullptr || rows <= 0 || row_elems <= 0 || row_elems % 8)
+    return fail(MUP_ERR_BAD_ARG, "bad gather arguments (row_elems must be a multiple of 8)");
+  if (reinterpret_cast<uintptr_t>(dst) % 16 || reinterpret_cast<uintptr_t>(src) % 16)
+    return fail(MUP_ERR_BAD_ARG, "gather buffers must be 16-byte aligned");
+  const int64_t vecs = row_elems / 8;
+  const int grid = synced_copy_grid(rows * vecs);
+  mup::SyncParams sp;
+  int rc = fill_sync(&sp, sync, static_cast<unsigned long long>(grid));
+  if (rc != MUP_OK) return rc;
+  gather_rows_synced_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(dst), static_cast<const uint4*>(src), index, rows, vecs, sp);
+  MUP_CUDA(cudaGetLastError());
+  return MUP_OK;
+}
+
+int mup_regroup_rows_synced(void* dst, const void* src, int up, int batch, int64_t seq,
+                            int64_t row_elems, int to_batch_major, void* stream, mup_sync* sync) {
+  if (dst == nullptr || src == nullptr || up <= 0 || batch <= 0 || seq <= 0 || row_elems <= 0 ||
+      row_elems % 8)
+    return fail(MUP_ERR_BAD_ARG, "bad regroup arguments (row_elems must be a multiple of 8)");
+  if (reinterpret_cast<uintptr_t>(dst) % 16 || reinterpret_cast<uintptr_t>(src) % 16)
+    return fail(MUP_ERR_BAD_ARG, "regroup buffers must be 16-byte aligned");
+  const int64_t vecs = row_elems / 8;
+  const int64_t total = static_cast<int64_t>(up) * batch * seq * vecs;
+  const int grid = synced_copy_grid(total);
+  mup::SyncParams sp;
+  int rc = fill_sync(&sp, sync, static_cast<unsigned long long>(grid));
+  if (rc != MUP_OK) return rc;
+  regroup_rows_synced_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(dst), static_cast<const uint4*>(src), up, batch, seq, vecs,
+      to_batch_major, sp);
   MUP_CUDA(cudaGetLastError());
   return MUP_OK;
 }

@@ -30,6 +30,7 @@
 #pragma once
 
 #include "mup_ptx.cuh"
+#include "mup_sync.cuh"
 
 namespace mup {
 
@@ -118,7 +119,8 @@ struct GemmParams {
   int pull_stride;                   // pull warps in the grid: distance between the tickets of a chunk
   int pull_rows;                     // rows per pull ticket: a power of two <= 16 with pull_rows * shard / 8 <= 512
   unsigned int flags;                // tuning switches (kFlag*)
-  unsigned long long* trace;         // optional [grid][8] cycle counters (nullptr: off)
+  unsigned long long* trace;         // optional [grid][16] cycle counters (nullptr: off)
+  SyncParams sync;                   // slot hand-off folded into this launch (flags[0] == nullptr: none)
 };
 
 // Per-CTA trace slots (SM cycles unless noted), written when GemmParams::trace is set.
@@ -397,6 +399,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     uint32_t store_it = 0;
     bool ok = true;
     long long epi_wait = 0;
+    bool handoff_checked = false;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++acc_it) {
       const int m_idx = tile / p.n_tiles;
       const int n_idx = tile - m_idx * p.n_tiles;
@@ -479,6 +482,23 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
         fence_proxy_async_smem();
         __syncwarp();
+        if constexpr (MODE == MODE_PEER_WRITE) {
+          // The slots may still be read by their owners (copy-out of the previous
+          // operation): the first store of this warp waits for their hand-off.
+          if (!handoff_checked) {
+            handoff_checked = true;
+            const bool handed = sync_wait_warp(p.sync, lane);
+            if (lane == 0) {
+              fence_proxy_async_all();  // the acquires above before the async-proxy stores below
+              if (!handed) *abort_flag = 1u;
+            }
+            __syncwarp();
+            if (!handed) {
+              ok = false;
+              break;
+            }
+          }
+        }
         if (lane == 0) {
           if (row0 < p.M && in_range) {
             if constexpr (MODE == MODE_PEER_WRITE) {
@@ -534,6 +554,12 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           red_release_gpu_add_u64(reinterpret_cast<uint64_t*>(p.ready + panel), 1ull);
         }
       };
+      // The peers' staged shards are handed off by the tail of their staging copy.
+      {
+        const bool handed = sync_wait_warp(p.sync, lane);
+        if (!handed && lane == 0) *abort_flag = 1u;
+        __syncwarp();
+      }
       int pending_panel = -1;
       int tickets_done = 0;
       // The first chunk of every pull warp is its own index (no atomic on the
@@ -589,6 +615,10 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         c = c_next;
       }
       if (pending_panel >= 0) publish(pending_panel);
+      // This warp will not read a peer arena again: once every pull warp of the
+      // grid has said so, the peers may reuse their arenas.
+      __syncwarp();
+      if (lane == 0) sync_arrive_and_signal(p.sync);
       if (trace && lane == 0) {
         atomicMax(trace + kTracePullEndNs, static_cast<unsigned long long>(globaltimer_ns()));
         atomicAdd(trace + kTracePullTickets, static_cast<unsigned long long>(tickets_done));
@@ -610,6 +640,14 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc<G>(tmem_base, kTmemCols);
+  }
+  if constexpr (MODE == MODE_PEER_WRITE) {
+    // Every store of this CTA has completed (bulk wait in the epilogue warps,
+    // then the barrier above): count the CTA in; the last one raises the flags.
+    if (threadIdx.x == 0) {
+      fence_proxy_async_global();
+      sync_arrive_and_signal(p.sync);
+    }
   }
   if (trace != nullptr && threadIdx.x == 0) {
     trace[kTraceEnd] = clock64();

@@ -64,13 +64,19 @@ class CompiledHeadShardPullGemm:
         _native.call("mup_pull_plan_reset", self._plan, handle)
         self.epoch = 0
 
-    def __call__(self, stream: torch.cuda.Stream | None = None) -> None:
+    def __call__(
+        self, stream: torch.cuda.Stream | None = None, sync: "_native.MupSync | None" = None
+    ) -> None:
         if self.epoch >= self.workspace_epochs:
             raise RuntimeError(
                 "pull workspace exhausted: call reset_workspace() before launching again"
             )
         handle = (stream or torch.cuda.current_stream(self._workspace.device)).cuda_stream
-        _native.call("mup_pull_launch", self._plan, handle)
+        if sync is None:
+            _native.call("mup_pull_launch", self._plan, handle)
+        else:
+            # the hand-off with the staging peers is folded into the kernel
+            _native.call("mup_pull_launch_synced", self._plan, handle, ctypes.byref(sync))
         self.epoch += 1
 
     def __del__(self) -> None:

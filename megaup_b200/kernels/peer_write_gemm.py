@@ -84,7 +84,7 @@ class PeerWriteLaunch:
         self.smem_bytes = smem.value
         self._out_spans = tuple(_span(out) for out in peer_outs)
 
-    def __call__(self, a: Tensor) -> None:
+    def __call__(self, a: Tensor, sync: "_native.MupSync | None" = None) -> None:
         a = _as_2d(a, "A")
         if tuple(a.shape) != (self.rows, self.in_features):
             raise ValueError(
@@ -96,7 +96,13 @@ class PeerWriteLaunch:
             if a_start < stop and start < a_stop:
                 raise ValueError("A overlaps an output slot")
         stream = torch.cuda.current_stream(a.device).cuda_stream
-        _native.call("mup_peer_write_launch", self._plan, a.data_ptr(), stream)
+        if sync is None:
+            _native.call("mup_peer_write_launch", self._plan, a.data_ptr(), stream)
+        else:
+            # the hand-off with the slots' owners is folded into the kernel
+            _native.call(
+                "mup_peer_write_launch_synced", self._plan, a.data_ptr(), stream, ctypes.byref(sync)
+            )
 
     def __del__(self) -> None:
         plan, self._plan = getattr(self, "_plan", None), None

@@ -552,7 +552,15 @@ class _PeerWriteBase:
     # phase 1: the GEMM whose epilogue stores into the peers' slots
     def _launch(self, x: Tensor) -> None:
         rows = _rows(self._kind, self._logical_shape())
-        self.launch(x.view(rows, self.in_features))
+        runtime = self.runtime
+        if runtime.fused_sync:
+            # the kernel waits for the slots' owners before its first store and
+            # raises the "written" flag itself when its last CTA is done
+            sync = runtime._next_handoff()
+            self.launch(x.view(rows, self.in_features), sync=sync)
+            runtime._done_value = int(sync.done_after)
+        else:
+            self.launch(x.view(rows, self.in_features))
 
     # phase 2: barrier, slots -> ordinary memory, barrier
     def _materialize(self, out: Tensor) -> None:
@@ -560,7 +568,9 @@ class _PeerWriteBase:
         shape = self._logical_shape()
         layout = self._layout()
         if layout is not None:
-            runtime.copy_peer_written_indexed(rows=shape[0], index=layout.to_thd_index, out=out)
+            runtime.copy_peer_written_indexed(
+                rows=shape[0], index=layout.to_thd_index, out=out, _fused=runtime.fused_sync
+            )
             return
         # SBHD rows are sequence-major and a THD slab is already in global
         # order, so both materialise like BSHD with B = 1.
@@ -571,6 +581,7 @@ class _PeerWriteBase:
             shard_heads=self._shard_heads,
             head_dim=self.head_dim,
             out=out.view(batch, up * sequence, self._shard_heads, self.head_dim),
+            _fused=runtime.fused_sync,
         )
 
     def __call__(self, x: Tensor, *, out: Tensor | None = None, validate_group: bool = True) -> Tensor:
@@ -981,18 +992,29 @@ class _PullBase:
                 rows=shape[0],
                 source=head_x.view(up * shape[0], self.in_features // up),
                 index=layout.to_source_major_index,
+                _fused=runtime.fused_sync,
             )
             return
         # Rank chunks follow each other along the leading axis for SBHD and a
         # THD slab, so both stage like BSHD with B = 1.
         batch, sequence = (shape[0], shape[1]) if self._kind == "bshd" else (1, _rows(self._kind, shape))
-        runtime.stage_head_parallel(head_x.view(batch, up * sequence, shard_heads, self.head_dim))
+        runtime.stage_head_parallel(
+            head_x.view(batch, up * sequence, shard_heads, self.head_dim), _fused=runtime.fused_sync
+        )
 
     # phase 2: pull + GEMM, then barrier so no peer's slot is reused too early
     def _launch(self) -> None:
-        stream = torch.cuda.current_stream(self.runtime.device)
-        self.compiled(stream=stream)
-        self.runtime.finish_pull()
+        runtime = self.runtime
+        stream = torch.cuda.current_stream(runtime.device)
+        if runtime.fused_sync:
+            # the pull workers wait for the peers' staging copies, and the last of
+            # them to finish hands every arena back, long before the GEMM ends
+            sync = runtime._next_handoff()
+            self.compiled(stream=stream, sync=sync)
+            runtime._done_value = int(sync.done_after)
+        else:
+            self.compiled(stream=stream)
+            runtime.finish_pull()
 
     def __call__(self, head_x: Tensor, *, validate_group: bool = True) -> Tensor:
         self._validate_call(head_x, validate_group)

@@ -264,3 +264,22 @@ def test_fd_exchange_world_size_2() -> None:
 
 def test_exchange_semantics_over_gloo_world_size_2() -> None:
     _spawn("sharded_oracle_exchange")
+
+
+def test_mega_up_alias_package_resolves_to_this_implementation() -> None:
+    import mega_up as alias
+    from mega_up.kernels.peer_write_gemm import PEER_TILE_N as tile
+    from mega_up.ops import _build_thd_layout as build
+    from mega_up.runtime import MegaUPRuntime as runtime_class
+
+    assert alias.initialize_runtime is mega_up.initialize_runtime
+    assert build is ops._build_thd_layout and runtime_class is MegaUPRuntime and tile == 256
+    for name in (
+        "initialize_runtime", "supports_shape", "unsupported_shape_reason", "prepare_thd_layout", "THDLayout",
+        "prepare_peer_write_gemm_bshd", "prepare_peer_write_gemm_sbhd", "prepare_peer_write_gemm_thd",
+        "prepare_headshard_pull_gemm_bshd", "prepare_headshard_pull_gemm_sbhd", "prepare_headshard_pull_gemm_thd",
+        "peer_write_gemm_bshd", "peer_write_gemm_sbhd", "peer_write_gemm_thd",
+        "headshard_pull_gemm_bshd", "headshard_pull_gemm_sbhd", "headshard_pull_gemm_thd",
+        "MegaUPRuntime", "DEFAULT_MAX_ROWS", "SUPPORTED_UP_DEGREES",
+    ):
+        assert hasattr(alias, name), name
