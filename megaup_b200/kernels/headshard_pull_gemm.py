@@ -65,13 +65,19 @@ class CompiledHeadShardPullGemm:
         self.epoch = 0
 
     def __call__(
-        self, stream: torch.cuda.Stream | None = None, sync: "_native.MupSync | None" = None
+        self,
+        stream: torch.cuda.Stream | None = None,
+        sync: "_native.MupSync | None" = None,
+        stream_handle: int | None = None,
     ) -> None:
         if self.epoch >= self.workspace_epochs:
             raise RuntimeError(
                 "pull workspace exhausted: call reset_workspace() before launching again"
             )
-        handle = (stream or torch.cuda.current_stream(self._workspace.device)).cuda_stream
+        if stream_handle is not None:
+            handle = stream_handle
+        else:
+            handle = (stream or torch.cuda.current_stream(self._workspace.device)).cuda_stream
         if sync is None:
             _native.call("mup_pull_launch", self._plan, handle)
         else:

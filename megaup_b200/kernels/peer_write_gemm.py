@@ -84,7 +84,9 @@ class PeerWriteLaunch:
         self.smem_bytes = smem.value
         self._out_spans = tuple(_span(out) for out in peer_outs)
 
-    def __call__(self, a: Tensor, sync: "_native.MupSync | None" = None) -> None:
+    def __call__(
+        self, a: Tensor, sync: "_native.MupSync | None" = None, stream_handle: int | None = None
+    ) -> None:
         a = _as_2d(a, "A")
         if tuple(a.shape) != (self.rows, self.in_features):
             raise ValueError(
@@ -95,7 +97,9 @@ class PeerWriteLaunch:
         for start, stop in self._out_spans:
             if a_start < stop and start < a_stop:
                 raise ValueError("A overlaps an output slot")
-        stream = torch.cuda.current_stream(a.device).cuda_stream
+        stream = (
+            stream_handle if stream_handle is not None else torch.cuda.current_stream(a.device).cuda_stream
+        )
         if sync is None:
             _native.call("mup_peer_write_launch", self._plan, a.data_ptr(), stream)
         else:

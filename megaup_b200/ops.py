@@ -557,10 +557,10 @@ class _PeerWriteBase:
             # the kernel waits for the slots' owners before its first store and
             # raises the "written" flag itself when its last CTA is done
             sync = runtime._next_handoff()
-            self.launch(x.view(rows, self.in_features), sync=sync)
+            self.launch(x.view(rows, self.in_features), sync=sync, stream_handle=runtime._stream())
             runtime._done_value = int(sync.done_after)
         else:
-            self.launch(x.view(rows, self.in_features))
+            self.launch(x.view(rows, self.in_features), stream_handle=runtime._stream())
 
     # phase 2: barrier, slots -> ordinary memory, barrier
     def _materialize(self, out: Tensor) -> None:
@@ -1005,15 +1005,15 @@ class _PullBase:
     # phase 2: pull + GEMM, then barrier so no peer's slot is reused too early
     def _launch(self) -> None:
         runtime = self.runtime
-        stream = torch.cuda.current_stream(runtime.device)
+        handle = runtime._stream()
         if runtime.fused_sync:
             # the pull workers wait for the peers' staging copies, and the last of
             # them to finish hands every arena back, long before the GEMM ends
             sync = runtime._next_handoff()
-            self.compiled(stream=stream, sync=sync)
+            self.compiled(sync=sync, stream_handle=handle)
             runtime._done_value = int(sync.done_after)
         else:
-            self.compiled(stream=stream)
+            self.compiled(stream_handle=handle)
             runtime.finish_pull()
 
     def __call__(self, head_x: Tensor, *, validate_group: bool = True) -> Tensor:

@@ -253,6 +253,7 @@ class MegaUPRuntime:
     _done_counter: Tensor | None = field(default=None, init=False, repr=False)
     _done_value: int = field(default=0, init=False, repr=False)
     _leased: bool = field(default=False, init=False, repr=False)
+    _leased_stream: int | None = field(default=None, init=False, repr=False)
     _lease_lock: threading.Lock = field(default_factory=threading.Lock, init=False, repr=False)
     _completion_event: torch.cuda.Event | None = field(default=None, init=False, repr=False)
 
@@ -277,7 +278,9 @@ class MegaUPRuntime:
         return _KERNEL_TIMEOUT_NS
 
     def _stream(self) -> int:
-        return torch.cuda.current_stream(self.device).cuda_stream
+        # inside a lease the operation's stream was looked up once, on entry
+        handle = self._leased_stream
+        return handle if handle is not None else torch.cuda.current_stream(self.device).cuda_stream
 
     @property
     def fused_sync(self) -> bool:
@@ -348,9 +351,11 @@ class MegaUPRuntime:
             previous = self._completion_event
         if previous is not None:
             stream.wait_event(previous)
+        self._leased_stream = stream.cuda_stream
         try:
             yield self
         finally:
+            self._leased_stream = None
             done = torch.cuda.Event()
             done.record(stream)
             with self._lease_lock:
