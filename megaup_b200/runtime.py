@@ -362,8 +362,13 @@ class MegaUPRuntime:
                 self._completion_event = done
                 self._leased = False
 
-    def barrier(self) -> None:
-        """All-peer slot hand-off on the current stream (reference: runtime.py:108-112)."""
+    def barrier(self, *, timeout_s: float | None = None) -> None:
+        """All-peer slot hand-off on the current stream (reference: runtime.py:108-112).
+
+        The device-side wait is bounded (``MEGA_UP_FLAG_TIMEOUT_S``, 30 s, or
+        ``timeout_s``): a peer that never arrives makes the kernel end with a
+        status code that ``check_status()`` raises, instead of hanging the GPU.
+        """
 
         if self.emulated:
             return  # one process drives every emulated rank on one stream
@@ -375,7 +380,7 @@ class MegaUPRuntime:
             self.local_rank,
             self._epoch & 0xFFFFFFFF,
             self.status_address,
-            _FLAG_TIMEOUT_NS,
+            _FLAG_TIMEOUT_NS if timeout_s is None else int(timeout_s * 1e9),
             self._stream(),
         )
 

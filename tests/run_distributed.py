@@ -221,6 +221,27 @@ def main() -> None:
     x = randn((1, 64, heads, dim), 800 + rank)
     check("pw after rejections", mega_up.peer_write_gemm_bshd(x, w, runtime, bias=b), baseline_peer_write("bshd", x, w, b, up, None), exact=False)
 
+    # ---- a peer that does not show up: the bounded flag wait runs out, the host raises,
+    # the context survives, and the group realigns once the late rank arrives
+    torch.cuda.synchronize(device)
+    dist.barrier()
+    if rank == 0:
+        runtime.barrier(timeout_s=0.05)
+        torch.cuda.synchronize(device)
+        try:
+            runtime.check_status()
+            failures.append("flag timeout was not reported")
+        except RuntimeError as error:
+            if "slot hand-off flag" not in str(error):
+                failures.append(f"unexpected timeout message: {error}")
+    dist.barrier()  # host-side: the late ranks arrive only after rank 0 has given up
+    if rank != 0:
+        runtime.barrier()
+    torch.cuda.synchronize(device)
+    runtime.check_status()
+    x = randn((1, 64, heads, dim), 850 + rank)
+    check("pw after a timed-out hand-off", mega_up.peer_write_gemm_bshd(x, w, runtime, bias=b), baseline_peer_write("bshd", x, w, b, up, None), exact=False)
+
     # ---- a second runtime with another hidden has its own arena
     other = mega_up.initialize_runtime(group, hidden=2 * hidden, max_rows=64, device=device)
     if other is runtime or other.arena.data_ptr() == runtime.arena.data_ptr():
