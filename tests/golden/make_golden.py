@@ -1,11 +1,11 @@
 """Generate the golden fixtures in this directory by RUNNING the reference.
 
-Needs the reference checkout (pass its path, default /root/reference); it is
+Needs a checkout of the reference (pass its path as the first argument); it is
 imported, never copied. Outputs are small compressed files committed next to
 this script. Inputs are not stored: tests regenerate them with
 ``golden_inputs`` below (numpy PCG64 streams, identical on every platform).
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 What is pinned:
   shape_rule.json       unsupported_shape_reason over a (width, UP) sweep
@@ -146,7 +146,9 @@ def _worker(rank: int, world: int, port: int, ref_root: str, out_dir: str) -> No
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref_root = sys.argv[1]
     sys.path.insert(0, ref_root)
     import torch
     import torch.multiprocessing as mp
