@@ -314,7 +314,7 @@ int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int 
   p.up = up;
   p.rank = rank;
   p.m_tiles = (rows + mup::kBlockM * g - 1) / (mup::kBlockM * g);
-  p.k_tiles = (k + mup::kBlockK - 1) / mup::kBlockK;
+  p.k_tiles = (k + mup::kStageK - 1) / mup::kStageK;
   int max_clusters = 0;
   if (g == 1) {
     rc = configure_kernel<1, MODE>(&max_clusters);
@@ -1063,7 +1063,7 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
     p.tile_n = choose_tile_n(p.m_tiles, n, slots);
   }
   p.n_tiles = (n + p.tile_n - 1) / p.tile_n;
-  p.k_tiles = (k + mup::kBlockK - 1) / mup::kBlockK;
+  p.k_tiles = (k + mup::kStageK - 1) / mup::kStageK;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.status = static_cast<uint32_t*>(status_device_ptr);
   p.timeout_ns = timeout_ns;

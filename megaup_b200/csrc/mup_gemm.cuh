@@ -36,7 +36,10 @@ namespace mup {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
-constexpr int kBlockK = 64;
+constexpr int kBlockK = 64;           // K extent of one TMA box (128 bytes, the swizzle span)
+constexpr int kKSub = 1;              // boxes per pipeline stage (2 = 128-K stages with 8 MMAs per barrier round:
+                                      // measured no faster, 3 deep stages hide less latency than 6 shallow ones)
+constexpr int kStageK = kBlockK * kKSub;
 constexpr int kUmmaK = 16;
 constexpr int kMaxPeers = 8;
 constexpr int kAccStages = 2;
@@ -86,7 +89,7 @@ struct GemmCfg {
 // W rows one CTA loads per stage, bytes of a stage, number of stages.
 __host__ __device__ constexpr int tile_b_rows(int tile_n, int g) { return tile_n / g; }
 __host__ __device__ constexpr int tile_stage_bytes(int tile_n, int g) {
-  return kBlockM * kBlockK * 2 + tile_b_rows(tile_n, g) * kBlockK * 2;
+  return kKSub * (kBlockM * kBlockK * 2 + tile_b_rows(tile_n, g) * kBlockK * 2);
 }
 __host__ __device__ constexpr int tile_stages(int tile_n, int g) {
   return kStageAreaBytes / tile_stage_bytes(tile_n, g) > kMaxStages
@@ -270,19 +273,29 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
             ok = false;
             break;
           }
+          // Stage layout: [A box 0][A box 1][B box 0][B box 1], every box 64 K elements wide.
           const uint32_t a_dst = smem_base + stage * stage_bytes;
-          const uint32_t b_dst = a_dst + Cfg::kABytes;
+          const uint32_t b_dst = a_dst + kKSub * Cfg::kABytes;
+          const uint32_t b_box_bytes = static_cast<uint32_t>(tile_b_rows(tile_n, G)) * kBlockK * 2;
           if constexpr (G == 1) {
             mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
-            tma_load_2d(a_dst, &p.map_a, kt * kBlockK, a_row0, full_bar(stage));
-            tma_load_2d(b_dst, &p.map_b, kt * kBlockK, b_row0, full_bar(stage));
+#pragma unroll
+            for (int sub = 0; sub < kKSub; ++sub) {
+              const int kcol = kt * kStageK + sub * kBlockK;
+              tma_load_2d(a_dst + sub * Cfg::kABytes, &p.map_a, kcol, a_row0, full_bar(stage));
+              tma_load_2d(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, full_bar(stage));
+            }
           } else {
             // Both CTAs' loads complete on the leader's barrier, which the
             // leader arms for the bytes of the whole pair.
             const uint32_t bar = leader_full0 + 8u * stage;
             if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * stage_bytes);
-            tma_load_2d_pair(a_dst, &p.map_a, kt * kBlockK, a_row0, bar);
-            tma_load_2d_pair(b_dst, &p.map_b, kt * kBlockK, b_row0, bar);
+#pragma unroll
+            for (int sub = 0; sub < kKSub; ++sub) {
+              const int kcol = kt * kStageK + sub * kBlockK;
+              tma_load_2d_pair(a_dst + sub * Cfg::kABytes, &p.map_a, kcol, a_row0, bar);
+              tma_load_2d_pair(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, bar);
+            }
           }
           if (in_flight < static_cast<uint32_t>(num_stages)) ++in_flight;
           if (++stage == static_cast<uint32_t>(num_stages)) {
@@ -320,6 +333,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     const uint32_t idesc = make_idesc_bf16(Cfg::kUmmaM, tile_n);
     const uint64_t desc0 = make_kmajor_sw128_desc(smem_base);
     const uint64_t desc_step = static_cast<uint64_t>(stage_bytes >> 4);
+    const uint64_t b_box_step = static_cast<uint64_t>((tile_b_rows(tile_n, G) * kBlockK * 2) >> 4);
     const bool pair_commit = (G == 2) && (p.flags & kFlagSplitCommit) == 0u;
     uint32_t stage = 0, phase = 0;
     uint32_t acc_it = 0;
@@ -345,13 +359,18 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (trace) wait_full += clock64() - t_full;
         tc_fence_after_sync();
         const uint64_t a_desc = desc0 + desc_step * stage;
-        const uint64_t b_desc = a_desc + static_cast<uint64_t>(Cfg::kABytes >> 4);
+        const uint64_t b_desc = a_desc + static_cast<uint64_t>((kKSub * Cfg::kABytes) >> 4);
         if (elect_one_sync()) {
-          // 16 BF16 = 32 bytes further along K inside the 128-byte swizzle row per step
-          umma_bf16<G>(d_tmem, a_desc, b_desc, idesc, kt > 0 ? 1u : 0u);
-          umma_bf16<G>(d_tmem, a_desc + 2, b_desc + 2, idesc, 1u);
-          umma_bf16<G>(d_tmem, a_desc + 4, b_desc + 4, idesc, 1u);
-          umma_bf16<G>(d_tmem, a_desc + 6, b_desc + 6, idesc, 1u);
+          // Per box: 16 BF16 = 32 bytes further along K inside the 128-byte swizzle row per MMA.
+#pragma unroll
+          for (int sub = 0; sub < kKSub; ++sub) {
+            const uint64_t a_sub = a_desc + static_cast<uint64_t>(sub) * (Cfg::kABytes >> 4);
+            const uint64_t b_sub = b_desc + static_cast<uint64_t>(sub) * b_box_step;
+            umma_bf16<G>(d_tmem, a_sub, b_sub, idesc, (kt > 0 || sub > 0) ? 1u : 0u);
+            umma_bf16<G>(d_tmem, a_sub + 2, b_sub + 2, idesc, 1u);
+            umma_bf16<G>(d_tmem, a_sub + 4, b_sub + 4, idesc, 1u);
+            umma_bf16<G>(d_tmem, a_sub + 6, b_sub + 6, idesc, 1u);
+          }
           // Release the shared-memory slot once these MMAs have read it.
           if constexpr (G == 1) {
             umma_commit_1(empty_bar(stage));
