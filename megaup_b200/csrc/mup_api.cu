@@ -273,10 +273,13 @@ int check_common(int device, int rows, int n, int k, int up, int rank, const voi
   return MUP_OK;
 }
 
-// Width of an output tile. A tcgen05.mma of M = 128 rows per SM occupies the
-// tensor pipe for 128 cycles whatever its N (measured: 256, 192, 128 and 64
-// columns all take 128 cycles), so a narrower tile only pays off when it
-// lowers the number of waves; ties go to the widest tile.
+// Width of an output tile. With N = 256 the K loop is bound by the tensor pipe
+// (128 cycles per tcgen05.mma of 128 rows per SM); narrower MMAs need fewer
+// pipe cycles but the issuing thread can only start one every ~90 cycles, so
+// 192- and 128-wide tiles are issue-bound (measured on the 4096 x 5120 x 5120
+// problem: 148.7 us at 256, 156.0 us at 192, 164.1 us at 128 in their best
+// configuration). A narrower tile therefore only pays off when it removes
+// whole waves; ties go to the widest tile.
 // MEGA_UP_TILE_N overrides the choice (tuning only).
 int choose_tile_n(int m_tiles, int n, int slots) {
   if (const char* env = getenv("MEGA_UP_TILE_N")) {

@@ -37,7 +37,10 @@ namespace mup {
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockK = 64;           // K extent of one TMA box (128 bytes, the swizzle span)
-constexpr int kKSub = 1;              // boxes per pipeline stage (2 = 128-K stages with 8 MMAs per barrier round:
+#ifndef MUP_KSUB
+#define MUP_KSUB 1
+#endif
+constexpr int kKSub = MUP_KSUB;              // boxes per pipeline stage (2 = 128-K stages with 8 MMAs per barrier round:
                                       // measured no faster, 3 deep stages hide less latency than 6 shallow ones)
 constexpr int kStageK = kBlockK * kKSub;
 constexpr int kUmmaK = 16;
@@ -141,6 +144,7 @@ constexpr int kTraceGateFirstNs = 10; // ns from kernel entry until the producer
 constexpr int kTraceGateCycles = 11;  // producer cycles spent at panel gates
 constexpr int kTraceSlots = 16;
 
+constexpr unsigned int kFlagNoL2Hints = 8u;     // tuning: drop the L2 hints (W loads evict-last, output stores evict-first)
 constexpr unsigned int kFlagSplitCommit = 1u;  // G=2: one commit per CTA of the pair instead of one for both
 
 __device__ __forceinline__ void report_status(const GemmParams& p, volatile uint32_t* abort_flag,
@@ -226,6 +230,8 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       bool ok = true;
       long long waited = 0;
       const uint32_t leader_full0 = (G == 2) ? mapa_cluster(full_bar(0), 0) : full_bar(0);
+      const bool hints = (p.flags & kFlagNoL2Hints) == 0u;
+      const uint64_t keep = l2_policy_evict_last();  // W is re-read by every wave of tiles
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const int m_idx = tile / p.n_tiles;
         const int n_idx = tile - m_idx * p.n_tiles;
@@ -283,7 +289,11 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
             for (int sub = 0; sub < kKSub; ++sub) {
               const int kcol = kt * kStageK + sub * kBlockK;
               tma_load_2d(a_dst + sub * Cfg::kABytes, &p.map_a, kcol, a_row0, full_bar(stage));
-              tma_load_2d(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, full_bar(stage));
+              if (hints) {
+                tma_load_2d_hint(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, full_bar(stage), keep);
+              } else {
+                tma_load_2d(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, full_bar(stage));
+              }
             }
           } else {
             // Both CTAs' loads complete on the leader's barrier, which the
@@ -294,7 +304,11 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
             for (int sub = 0; sub < kKSub; ++sub) {
               const int kcol = kt * kStageK + sub * kBlockK;
               tma_load_2d_pair(a_dst + sub * Cfg::kABytes, &p.map_a, kcol, a_row0, bar);
-              tma_load_2d_pair(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, bar);
+              if (hints) {
+                tma_load_2d_pair_hint(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, bar, keep);
+              } else {
+                tma_load_2d_pair(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, bar);
+              }
             }
           }
           if (in_flight < static_cast<uint32_t>(num_stages)) ++in_flight;
@@ -326,9 +340,10 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   // --------------------------------------------------------------- MMA issue
   // The whole warp runs this loop in lock-step and one elected lane issues the
   // tcgen05 instructions: with warp-uniform control flow the descriptors stay
-  // in uniform registers and an iteration costs ~50 cycles on top of the four
-  // 128-cycle MMAs; a loop run by a single lane inside a divergent branch
-  // measured ~250 cycles of overhead per K step and starved the tensor pipe.
+  // in uniform registers, the issuing thread needs ~560 cycles per K step
+  // (4 issues of ~97 cycles, ~170 for barrier poll, fence and commit) against
+  // 512 cycles of tensor-pipe work; a loop run by a single lane inside a
+  // divergent branch needed ~770 and starved the pipe.
   if (warp == 1 && !misaligned && cta_rank == 0) {
     const uint32_t idesc = make_idesc_bf16(Cfg::kUmmaM, tile_n);
     const uint64_t desc0 = make_kmajor_sw128_desc(smem_base);
@@ -523,9 +538,17 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
             if constexpr (MODE == MODE_PEER_WRITE) {
               const int dst = gcol / p.shard;
               const int lcol = gcol - dst * p.shard;
-              tma_store_2d(&p.map_out[dst], lcol, row0, smem_u32(buf));
+              if ((p.flags & kFlagNoL2Hints) == 0u) {
+                tma_store_2d_hint(&p.map_out[dst], lcol, row0, smem_u32(buf), l2_policy_evict_first());
+              } else {
+                tma_store_2d(&p.map_out[dst], lcol, row0, smem_u32(buf));
+              }
             } else {
-              tma_store_2d(&p.map_out[0], gcol, row0, smem_u32(buf));
+              if ((p.flags & kFlagNoL2Hints) == 0u) {
+                tma_store_2d_hint(&p.map_out[0], gcol, row0, smem_u32(buf), l2_policy_evict_first());
+              } else {
+                tma_store_2d(&p.map_out[0], gcol, row0, smem_u32(buf));
+              }
             }
           }
           bulk_commit_group();
