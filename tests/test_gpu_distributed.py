@@ -20,15 +20,22 @@ def _group_size() -> int:
     return 8 if count >= 8 else 4 if count >= 4 else 2 if count >= 2 else 0
 
 
-def test_fused_operators_match_cublas_plus_nccl() -> None:
+@pytest.mark.parametrize("handoff", ["barrier_kernels", "folded_into_kernels"])
+def test_fused_operators_match_cublas_plus_nccl(handoff: str) -> None:
+    """Both slot hand-off protocols: two stand-alone barrier kernels per operation (the
+    default) and the hand-off folded into the producing / consuming kernels."""
+
+    import os
+
     up = _group_size()
     if up == 0:
         pytest.skip("needs at least 2 GPUs")
+    env = dict(os.environ, MEGA_UP_FUSED_SYNC="1" if handoff == "folded_into_kernels" else "0")
     command = [
         sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={up}",
         "--master-addr", "127.0.0.1", "--master-port", "29533", str(ROOT / "tests" / "run_distributed.py"),
     ]
-    result = subprocess.run(command, capture_output=True, text=True, timeout=900, cwd=ROOT)
+    result = subprocess.run(command, capture_output=True, text=True, timeout=900, cwd=ROOT, env=env)
     lines = [line for line in result.stdout.splitlines() if line.startswith("[CORRECTNESS_RESULT]")]
     assert result.returncode == 0 and lines, result.stdout[-4000:] + result.stderr[-4000:]
     report = json.loads(lines[-1].split(" ", 1)[1])
