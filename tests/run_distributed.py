@@ -90,6 +90,10 @@ def baseline_pull(kind, head_x, w, b, up, cu):
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--full", action="store_true", help="also run the Wan2.1-14B-shaped configuration")
+    parser.add_argument(
+        "--stress", type=int, default=0,
+        help="with --full: this many extra back-to-back peer-write + pull rounds on fresh inputs, every result checked",
+    )
     args = parser.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local_rank = int(os.environ.get("LOCAL_RANK", rank))
@@ -262,6 +266,34 @@ def main() -> None:
         check("pull Wan2.1-14B O", out, want)
         torch.cuda.synchronize(device)
         big_rt.check_status()
+        # back-to-back rounds on fresh inputs: the slots are reused immediately, so a
+        # hand-off that lets a rank run ahead would show up as stale or torn rows
+        if args.stress:
+            writer = mega_up.prepare_peer_write_gemm_bshd(
+                wq, big_rt, batch=1, sequence=tokens, heads=big_heads, head_dim=128, bias=bq
+            )
+            bad_rounds = 0
+            for round_index in range(args.stress):
+                x = randn((1, tokens, big_heads, 128), 2000 + 16 * round_index + rank)
+                hx = randn((1, up * tokens, big_heads // up, 128), 6000 + 16 * round_index + rank)
+                got_pw = writer(x, validate_group=False)
+                got_pull = pull(hx, validate_group=False).clone()
+                got_mat = pull.materialized_input.clone()
+                want_pw = baseline_peer_write("bshd", x, wq, bq, up, None)
+                mat, want_pull = baseline_pull("bshd", hx, wq, bq, up, None)
+                same = (
+                    torch.equal(got_pw.reshape(want_pw.shape), want_pw)
+                    and torch.equal(got_mat, mat)
+                    and torch.equal(got_pull.reshape(want_pull.shape), want_pull)
+                )
+                bad_rounds += 0 if same else 1
+            worst = torch.tensor([bad_rounds], device=device)
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            report["stress"] = {"rounds": args.stress, "bad_rounds": int(worst[0])}
+            if int(worst[0]):
+                failures.append("stress rounds")
+            torch.cuda.synchronize(device)
+            big_rt.check_status()
 
     torch.cuda.synchronize(device)
     report["failures"] = failures
