@@ -273,13 +273,14 @@ int check_common(int device, int rows, int n, int k, int up, int rank, const voi
   return MUP_OK;
 }
 
-// Width of an output tile. With N = 256 the K loop is bound by the tensor pipe
-// (128 cycles per tcgen05.mma of 128 rows per SM); narrower MMAs need fewer
-// pipe cycles but the issuing thread can only start one every ~90 cycles, so
-// 192- and 128-wide tiles are issue-bound (measured on the 4096 x 5120 x 5120
-// problem: 148.7 us at 256, 156.0 us at 192, 164.1 us at 128 in their best
-// configuration). A narrower tile therefore only pays off when it removes
-// whole waves; ties go to the widest tile.
+// Width of an output tile. Every SM reads (128 + tile_n / 2) operand rows per
+// tile_n output columns of its 128 rows (CTA pair), so the L2 -> SM traffic of
+// the whole GEMM is 1.68 GB at 256, 1.96 GB at 192 and 2.52 GB at 128 for the
+// 4096 x 5120 x 5120 problem. Measured, all three widths move ~11-12 TB/s and
+// take 149 / 162 / 206 us: below 256 the kernel is bound by that traffic, not
+// by the tensor pipe (in isolation, on resident operands, the issue sequence
+// keeps the pipe full at every width). A narrower tile therefore only pays off
+// when it removes whole waves; ties go to the widest tile.
 // MEGA_UP_TILE_N overrides the choice (tuning only).
 int choose_tile_n(int m_tiles, int n, int slots) {
   if (const char* env = getenv("MEGA_UP_TILE_N")) {
@@ -300,6 +301,22 @@ int choose_tile_n(int m_tiles, int n, int slots) {
     }
   }
   return best;
+}
+
+// The last wave of the static schedule is usually partly filled (640 tiles on
+// 148 SMs: 4.32 waves). When it is at most half full, each of its tiles is run
+// as two half-width work items: about twice as many SMs work for half as
+// long. Half items read more of A per output column (the L2 -> SM traffic per
+// flop goes up by half), which is why only the tail is cut.
+// MEGA_UP_SPLIT_TAIL=0 turns the split off (tuning only).
+int choose_split_tiles(long long tiles, int slots, int tile_n) {
+  if (const char* env = getenv("MEGA_UP_SPLIT_TAIL")) {
+    if (atoi(env) == 0) return 0;
+  }
+  if (mup::kKSub != 1 || (tile_n != 256 && tile_n != 128)) return 0;
+  const long long rem = tiles % slots;
+  if (rem == 0 || 2 * rem > slots) return 0;
+  return static_cast<int>(rem);
 }
 
 // Fill the geometry shared by both modes and size the grid.
@@ -325,7 +342,9 @@ int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int 
     p.tile_n = choose_tile_n(p.m_tiles, n, info.sms);
     p.n_tiles = (n + p.tile_n - 1) / p.tile_n;
     const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
-    core->grid = static_cast<int>(tiles < info.sms ? tiles : info.sms);
+    p.split_tiles = choose_split_tiles(tiles, info.sms, p.tile_n);
+    const long long items = tiles + p.split_tiles;
+    core->grid = static_cast<int>(items < info.sms ? items : info.sms);
     core->smem_bytes = mup::GemmCfg<1>::kSmemBytes;
   } else {
     rc = configure_kernel<2, MODE>(&max_clusters);
@@ -336,7 +355,9 @@ int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int 
     p.tile_n = choose_tile_n(p.m_tiles, n, clusters);
     p.n_tiles = (n + p.tile_n - 1) / p.tile_n;
     const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
-    if (tiles < clusters) clusters = static_cast<int>(tiles);
+    p.split_tiles = choose_split_tiles(tiles, clusters, p.tile_n);
+    const long long items = tiles + p.split_tiles;
+    if (items < clusters) clusters = static_cast<int>(items);
     core->grid = clusters * 2;
     core->smem_bytes = mup::GemmCfg<2>::kSmemBytes;
   }
@@ -762,6 +783,7 @@ int mup_peer_write_plan_create(mup_peer_write_plan** out, int device, int rows, 
     p.status = static_cast<uint32_t*>(status_device_ptr);
     p.timeout_ns = timeout_ns;
     rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, p.tile_n / g);
+    if (rc == MUP_OK) rc = encode_map(&p.map_b_half, weight, k, n, k, mup::kBlockK, p.tile_n / (2 * g));
     for (int d = 0; d < up && rc == MUP_OK; ++d) {
       if (slot_ptrs[d] == nullptr) rc = fail(MUP_ERR_BAD_ARG, "slot pointer %d is null", d);
       if (rc == MUP_OK)
@@ -875,6 +897,7 @@ int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k
     }
     if (rc == MUP_OK) rc = encode_map(&p.map_a, dy, k, rows, k, mup::kBlockK, mup::kBlockM);
     if (rc == MUP_OK) rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, p.tile_n / g);
+    if (rc == MUP_OK) rc = encode_map(&p.map_b_half, weight, k, n, k, mup::kBlockK, p.tile_n / (2 * g));
     if (rc == MUP_OK)
       rc = encode_map(&p.map_out[0], out_buf, n, rows, n, mup::kEpiCols, mup::kEpiRows);
     plan->workspace = workspace;

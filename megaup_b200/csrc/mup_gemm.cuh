@@ -103,6 +103,7 @@ __host__ __device__ constexpr int tile_stages(int tile_n, int g) {
 struct GemmParams {
   CUtensorMap map_a;                 // A  [M, K]   box 64 x 128
   CUtensorMap map_b;                 // W  [N, K]   box 64 x (tile_n/G)
+  CUtensorMap map_b_half;            // W  [N, K]   box 64 x (tile_n/2G), for the split tail tiles
   CUtensorMap map_out[kMaxPeers];    // peer-write: [rows, shard] slot in peer p; pull: [0] = out [M, N]
   const __nv_bfloat16* bias;         // nullptr when absent
   uint32_t* status;                  // error word (host-visible)
@@ -113,6 +114,7 @@ struct GemmParams {
   int n_rot;                         // peer-write: first N tile of this rank
   int m_tiles, n_tiles, k_tiles;     // m_tiles counts (128*G)-row tiles, n_tiles tile_n-column tiles
   int tile_n;                        // 128, 192 or 256 output columns per tile
+  int split_tiles;                   // this many trailing tiles are each run as two half-width tiles (0: none)
   // pull mode only
   const __nv_bfloat16* peers[kMaxPeers];  // staged arenas [up(dest), peer_rows, shard]
   __nv_bfloat16* dy;                 // dense pulled input [M, K]
@@ -146,6 +148,7 @@ constexpr int kTraceSlots = 16;
 
 constexpr unsigned int kFlagNoL2Hints = 8u;     // tuning: drop the L2 hints (W loads evict-last, output stores evict-first)
 constexpr unsigned int kFlagSplitCommit = 1u;  // G=2: one commit per CTA of the pair instead of one for both
+constexpr unsigned int kFlagSeparateIssue = 2u;  // tuning: poll, MMAs and commit as separate statements (the slower issue loop)
 
 __device__ __forceinline__ void report_status(const GemmParams& p, volatile uint32_t* abort_flag,
                                               uint32_t code, uint32_t detail) {
@@ -174,6 +177,27 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   const int tile_n = p.tile_n;
   const int num_stages = tile_stages(tile_n, G);
   const uint32_t stage_bytes = static_cast<uint32_t>(tile_stage_bytes(tile_n, G));
+  // Work items: the tiles of the full waves, then the tiles of the last,
+  // partly filled wave cut into two half-width items each, so that the tail
+  // keeps about twice as many SMs busy for half as long. An item keeps the
+  // whole K loop of its columns, so the accumulation order is unchanged.
+  const int split_from = num_tiles - p.split_tiles;
+  const int num_items = num_tiles + p.split_tiles;
+  auto decode_item = [&](int item, int& m_idx, int& n0, int& width) {
+    int t = item;
+    int half = 0;
+    width = tile_n;
+    if (item >= split_from) {
+      const int j = item - split_from;
+      t = split_from + (j >> 1);
+      half = j & 1;
+      width = tile_n >> 1;
+    }
+    m_idx = t / p.n_tiles;
+    int n_blk = t - m_idx * p.n_tiles + p.n_rot;
+    if (n_blk >= p.n_tiles) n_blk -= p.n_tiles;
+    n0 = n_blk * tile_n + half * width;
+  };
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_base = smem_base + Cfg::kOffBar;
@@ -232,14 +256,15 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t leader_full0 = (G == 2) ? mapa_cluster(full_bar(0), 0) : full_bar(0);
       const bool hints = (p.flags & kFlagNoL2Hints) == 0u;
       const uint64_t keep = l2_policy_evict_last();  // W is re-read by every wave of tiles
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int m_idx = tile / p.n_tiles;
-        const int n_idx = tile - m_idx * p.n_tiles;
-        int n_blk = n_idx + p.n_rot;
-        if (n_blk >= p.n_tiles) n_blk -= p.n_tiles;
+      for (int tile = cluster_id; tile < num_items && ok; tile += num_clusters) {
+        int m_idx, n0, width;
+        decode_item(tile, m_idx, n0, width);
         const int panel = m_idx * G + static_cast<int>(cta_rank);
         const int a_row0 = panel * kBlockM;
-        const int b_row0 = n_blk * tile_n + static_cast<int>(cta_rank) * tile_b_rows(tile_n, G);
+        const int b_rows = tile_b_rows(width, G);
+        const int b_row0 = n0 + static_cast<int>(cta_rank) * b_rows;
+        const CUtensorMap* map_b = (width == tile_n) ? &p.map_b : &p.map_b_half;
+        const uint32_t item_bytes = static_cast<uint32_t>(tile_stage_bytes(width, G));
         if constexpr (MODE == MODE_PULL) {
           // Gate on the pull workers having finished this 128-row panel.
           const int groups_per_panel = kBlockM / p.pull_rows;
@@ -282,32 +307,32 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           // Stage layout: [A box 0][A box 1][B box 0][B box 1], every box 64 K elements wide.
           const uint32_t a_dst = smem_base + stage * stage_bytes;
           const uint32_t b_dst = a_dst + kKSub * Cfg::kABytes;
-          const uint32_t b_box_bytes = static_cast<uint32_t>(tile_b_rows(tile_n, G)) * kBlockK * 2;
+          const uint32_t b_box_bytes = static_cast<uint32_t>(b_rows) * kBlockK * 2;
           if constexpr (G == 1) {
-            mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
+            mbar_arrive_expect_tx(full_bar(stage), item_bytes);
 #pragma unroll
             for (int sub = 0; sub < kKSub; ++sub) {
               const int kcol = kt * kStageK + sub * kBlockK;
               tma_load_2d(a_dst + sub * Cfg::kABytes, &p.map_a, kcol, a_row0, full_bar(stage));
               if (hints) {
-                tma_load_2d_hint(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, full_bar(stage), keep);
+                tma_load_2d_hint(b_dst + sub * b_box_bytes, map_b, kcol, b_row0, full_bar(stage), keep);
               } else {
-                tma_load_2d(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, full_bar(stage));
+                tma_load_2d(b_dst + sub * b_box_bytes, map_b, kcol, b_row0, full_bar(stage));
               }
             }
           } else {
             // Both CTAs' loads complete on the leader's barrier, which the
             // leader arms for the bytes of the whole pair.
             const uint32_t bar = leader_full0 + 8u * stage;
-            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * stage_bytes);
+            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * item_bytes);
 #pragma unroll
             for (int sub = 0; sub < kKSub; ++sub) {
               const int kcol = kt * kStageK + sub * kBlockK;
               tma_load_2d_pair(a_dst + sub * Cfg::kABytes, &p.map_a, kcol, a_row0, bar);
               if (hints) {
-                tma_load_2d_pair_hint(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, bar, keep);
+                tma_load_2d_pair_hint(b_dst + sub * b_box_bytes, map_b, kcol, b_row0, bar, keep);
               } else {
-                tma_load_2d_pair(b_dst + sub * b_box_bytes, &p.map_b, kcol, b_row0, bar);
+                tma_load_2d_pair(b_dst + sub * b_box_bytes, map_b, kcol, b_row0, bar);
               }
             }
           }
@@ -339,24 +364,34 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
 
   // --------------------------------------------------------------- MMA issue
   // The whole warp runs this loop in lock-step and one elected lane issues the
-  // tcgen05 instructions: with warp-uniform control flow the descriptors stay
-  // in uniform registers, the issuing thread needs ~560 cycles per K step
-  // (4 issues of ~97 cycles, ~170 for barrier poll, fence and commit) against
-  // 512 cycles of tensor-pipe work; a loop run by a single lane inside a
-  // divergent branch needed ~770 and starved the pipe.
+  // tcgen05 instructions. Measured in isolation on resident operands (SM cycles
+  // per 64-wide K step, 512 of them tensor-pipe work at N = 256): ~770 for a loop
+  // run by a single lane inside a divergent branch, ~560 for the warp-uniform
+  // loop with poll, four MMAs and commit as separate statements, 512 for the
+  // fused sequence used here (umma_kstep4_probe_next), which also keeps the pipe
+  // full at N = 128. In the full kernel the last step makes no measurable
+  // difference: the K loop is then limited by operand delivery from L2.
   if (warp == 1 && !misaligned && cta_rank == 0) {
-    const uint32_t idesc = make_idesc_bf16(Cfg::kUmmaM, tile_n);
+    const uint32_t idesc_full = make_idesc_bf16(Cfg::kUmmaM, tile_n);
+    const uint32_t idesc_half = make_idesc_bf16(Cfg::kUmmaM, tile_n >> 1);
     const uint64_t desc0 = make_kmajor_sw128_desc(smem_base);
     const uint64_t desc_step = static_cast<uint64_t>(stage_bytes >> 4);
-    const uint64_t b_box_step = static_cast<uint64_t>((tile_b_rows(tile_n, G) * kBlockK * 2) >> 4);
     const bool pair_commit = (G == 2) && (p.flags & kFlagSplitCommit) == 0u;
+    // The fused step needs one TMA box per stage and, for a CTA pair, the commit
+    // that reaches both CTAs' barriers at once.
+    const bool fused_step = (kKSub == 1) && (G == 1 || pair_commit) && (p.flags & kFlagSeparateIssue) == 0u;
     uint32_t stage = 0, phase = 0;
     uint32_t acc_it = 0;
     bool failed = false;
+    bool stage_ready = false;  // the probe of the previous step found this stage full
     long long wait_full = 0, wait_acc = 0;
-    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++acc_it) {
+    for (int tile = cluster_id; tile < num_items; tile += num_clusters, ++acc_it) {
       const uint32_t as = acc_it & 1u;
       const uint32_t aphase = (acc_it >> 1) & 1u;
+      const bool half_item = tile >= split_from;
+      const uint32_t idesc = half_item ? idesc_half : idesc_full;
+      const uint64_t b_box_step =
+          static_cast<uint64_t>((tile_b_rows(half_item ? (tile_n >> 1) : tile_n, G) * kBlockK * 2) >> 4);
       const long long t_acc = trace ? clock64() : 0;
       if (!mbar_wait_bounded(acc_empty_bar(as), aphase ^ 1u, abort_flag, timeout_ns)) {
         report_status(p, abort_flag, ST_MMA_ACC_TIMEOUT, static_cast<uint32_t>(tile));
@@ -366,40 +401,57 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + as * kBlockN;
       for (int kt = 0; kt < p.k_tiles; ++kt) {
-        const long long t_full = trace ? clock64() : 0;
-        if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, timeout_ns)) {
-          report_status(p, abort_flag, ST_MMA_FULL_TIMEOUT, static_cast<uint32_t>(tile));
-          failed = true;
+        if (!stage_ready) {
+          const long long t_full = trace ? clock64() : 0;
+          if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, timeout_ns)) {
+            report_status(p, abort_flag, ST_MMA_FULL_TIMEOUT, static_cast<uint32_t>(tile));
+            failed = true;
+          }
+          if (trace) wait_full += clock64() - t_full;
+          tc_fence_after_sync();
         }
-        if (trace) wait_full += clock64() - t_full;
-        tc_fence_after_sync();
         const uint64_t a_desc = desc0 + desc_step * stage;
         const uint64_t b_desc = a_desc + static_cast<uint64_t>((kKSub * Cfg::kABytes) >> 4);
-        if (elect_one_sync()) {
-          // Per box: 16 BF16 = 32 bytes further along K inside the 128-byte swizzle row per MMA.
+        uint32_t next_stage = stage + 1u, next_phase = phase;
+        if (next_stage == static_cast<uint32_t>(num_stages)) {
+          next_stage = 0;
+          next_phase ^= 1u;
+        }
+        if (fused_step) {
+          // Four MMAs, the commit that frees the stage and a probe of the next
+          // stage's barrier as one instruction sequence of the elected lane.
+          uint32_t probed = 0;
+          if (elect_one_sync()) {
+            probed = umma_kstep4_probe_next<G>(d_tmem, a_desc, b_desc, idesc, kt > 0 ? 1u : 0u, empty_bar(stage),
+                                               full_bar(next_stage), next_phase);
+          }
+          stage_ready = __any_sync(0xffffffffu, probed != 0u);
+        } else {
+          if (elect_one_sync()) {
+            // Per box: 16 BF16 = 32 bytes further along K inside the 128-byte swizzle row per MMA.
 #pragma unroll
-          for (int sub = 0; sub < kKSub; ++sub) {
-            const uint64_t a_sub = a_desc + static_cast<uint64_t>(sub) * (Cfg::kABytes >> 4);
-            const uint64_t b_sub = b_desc + static_cast<uint64_t>(sub) * b_box_step;
-            umma_bf16<G>(d_tmem, a_sub, b_sub, idesc, (kt > 0 || sub > 0) ? 1u : 0u);
-            umma_bf16<G>(d_tmem, a_sub + 2, b_sub + 2, idesc, 1u);
-            umma_bf16<G>(d_tmem, a_sub + 4, b_sub + 4, idesc, 1u);
-            umma_bf16<G>(d_tmem, a_sub + 6, b_sub + 6, idesc, 1u);
+            for (int sub = 0; sub < kKSub; ++sub) {
+              const uint64_t a_sub = a_desc + static_cast<uint64_t>(sub) * (Cfg::kABytes >> 4);
+              const uint64_t b_sub = b_desc + static_cast<uint64_t>(sub) * b_box_step;
+              umma_bf16<G>(d_tmem, a_sub, b_sub, idesc, (kt > 0 || sub > 0) ? 1u : 0u);
+              umma_bf16<G>(d_tmem, a_sub + 2, b_sub + 2, idesc, 1u);
+              umma_bf16<G>(d_tmem, a_sub + 4, b_sub + 4, idesc, 1u);
+              umma_bf16<G>(d_tmem, a_sub + 6, b_sub + 6, idesc, 1u);
+            }
+            // Release the shared-memory slot once these MMAs have read it.
+            if constexpr (G == 1) {
+              umma_commit_1(empty_bar(stage));
+            } else if (pair_commit) {
+              umma_commit_2_mask(empty_bar(stage), 3);
+            } else {
+              umma_commit_2(mapa_cluster(empty_bar(stage), 0));
+              umma_commit_2(mapa_cluster(empty_bar(stage), 1));
+            }
           }
-          // Release the shared-memory slot once these MMAs have read it.
-          if constexpr (G == 1) {
-            umma_commit_1(empty_bar(stage));
-          } else if (pair_commit) {
-            umma_commit_2_mask(empty_bar(stage), 3);
-          } else {
-            umma_commit_2(mapa_cluster(empty_bar(stage), 0));
-            umma_commit_2(mapa_cluster(empty_bar(stage), 1));
-          }
+          stage_ready = false;
         }
-        if (++stage == static_cast<uint32_t>(num_stages)) {
-          stage = 0;
-          phase ^= 1u;
-        }
+        stage = next_stage;
+        phase = next_phase;
       }
       // Publish the finished accumulator to the epilogue warps.
       if (elect_one_sync()) {
@@ -434,11 +486,9 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     bool ok = true;
     long long epi_wait = 0;
     bool handoff_checked = false;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++acc_it) {
-      const int m_idx = tile / p.n_tiles;
-      const int n_idx = tile - m_idx * p.n_tiles;
-      int n_blk = n_idx + p.n_rot;
-      if (n_blk >= p.n_tiles) n_blk -= p.n_tiles;
+    for (int tile = cluster_id; tile < num_items && ok; tile += num_clusters, ++acc_it) {
+      int m_idx, n0, width;
+      decode_item(tile, m_idx, n0, width);
       const uint32_t as = acc_it & 1u;
       const uint32_t aphase = (acc_it >> 1) & 1u;
       const int row0 = (m_idx * G + static_cast<int>(cta_rank)) * kBlockM + q * kEpiRows;
@@ -453,10 +503,9 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       tc_fence_after_sync();
 
-#pragma unroll 1
-      const int chunks = tile_n / kEpiCols;
+      const int chunks = width / kEpiCols;
       for (int c = 0; c < chunks; ++c) {
-        const int gcol = n_blk * tile_n + c * kEpiCols;
+        const int gcol = n0 + c * kEpiCols;
         const bool in_range = gcol < p.N;  // the last tile of a row may hang over N
         // Bias for these 64 columns, widened to FP32, shared inside the warp.
         if (p.bias != nullptr && in_range) {

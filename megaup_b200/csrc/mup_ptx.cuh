@@ -317,6 +317,73 @@ __device__ __forceinline__ void umma_commit_2_mask(uint32_t bar, uint16_t cta_ma
       : "memory");
 }
 
+// One 64-wide K step of the main loop as a single instruction sequence for the
+// issuing thread: a non-blocking test of the NEXT stage's full barrier is
+// issued first, then the four 16-wide MMAs of this stage and the commit that
+// releases it; the test's result is read only after the commit, so the
+// barrier round trip (~70 cycles for a thread that does nothing else) overlaps
+// the MMA issue slots instead of adding to them. Returns non-zero when the
+// next stage was already full.
+template <int G>
+__device__ __forceinline__ uint32_t umma_kstep4_probe_next(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                           uint32_t idesc, uint32_t accumulate_first,
+                                                           uint32_t commit_bar, uint32_t next_full_bar,
+                                                           uint32_t next_parity) {
+  uint32_t next_ready;
+  if constexpr (G == 1) {
+    asm volatile(
+        "{\n"
+        ".reg .pred pn, pa;\n"
+        ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 pn, [%7], %8;\n"
+        "setp.ne.b32 pa, %5, 0;\n"
+        "add.u64 a1, %2, 2;\n"
+        "add.u64 b1, %3, 2;\n"
+        "add.u64 a2, %2, 4;\n"
+        "add.u64 b2, %3, 4;\n"
+        "add.u64 a3, %2, 6;\n"
+        "add.u64 b3, %3, 6;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, pa;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a1, b1, %4, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a2, b2, %4, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a3, b3, %4, 1;\n"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n"
+        "selp.u32 %0, 1, 0, pn;\n"
+        "}\n"
+        : "=r"(next_ready)
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(commit_bar),
+          "r"(next_full_bar), "r"(next_parity)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred pn, pa;\n"
+        ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+        ".reg .b16 both;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 pn, [%7], %8;\n"
+        "setp.ne.b32 pa, %5, 0;\n"
+        "mov.b16 both, 3;\n"
+        "add.u64 a1, %2, 2;\n"
+        "add.u64 b1, %3, 2;\n"
+        "add.u64 a2, %2, 4;\n"
+        "add.u64 b2, %3, 4;\n"
+        "add.u64 a3, %2, 6;\n"
+        "add.u64 b3, %3, 6;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %4, pa;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], a1, b1, %4, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], a2, b2, %4, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], a3, b3, %4, 1;\n"
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%6], both;\n"
+        "selp.u32 %0, 1, 0, pn;\n"
+        "}\n"
+        : "=r"(next_ready)
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(commit_bar),
+          "r"(next_full_bar), "r"(next_parity)
+        : "memory");
+  }
+  return next_ready;
+}
+
 // 32 lanes x 32 consecutive FP32 columns: thread t of the warp receives row
 // (lane quarter base + t), registers = columns.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
