@@ -119,6 +119,33 @@ def test_pull_kernel(rows, n, k, up, rank, cta_group) -> None:
                 assert h.ulp_distance(out, ref) <= 1
 
 
+@pytest.mark.parametrize("rows,n,k,up,rank", [(4096, 5120, 5120, 8, 5), (640, 2304, 1024, 2, 1), (200, 1024, 1040, 8, 3)])
+def test_the_schedule_never_changes_a_bit(rows, n, k, up, rank, monkeypatch) -> None:
+    """Tile width, the half-width items of the last wave and the issue sequence
+    only decide which SM computes which columns when: every K loop stays whole
+    and ascending, so all variants must give identical bits."""
+
+    x = h.seeded((rows, k), 71, ints=False)
+    w, b = _weights(n, k, 72, False)
+    # the pull GEMM contracts over the exchanged width, which must obey the shape rule: use n
+    peers = [h.seeded((up, rows, n // up), 80 + p, ints=False) for p in range(up)]
+    w_pull, b_pull = _weights(n, n, 73, False)
+    results = []
+    variants = [{}, {"MEGA_UP_SPLIT_TAIL": "0"}, {"MEGA_UP_TILE_N": "128"}, {"MEGA_UP_TILE_N": "192", "MEGA_UP_KERNEL_FLAGS": "2"}]
+    for env in variants:
+        for name in ("MEGA_UP_SPLIT_TAIL", "MEGA_UP_TILE_N", "MEGA_UP_KERNEL_FLAGS"):
+            monkeypatch.delenv(name, raising=False)
+        for name, value in env.items():
+            monkeypatch.setenv(name, value)
+        slots, clean = h.run_peer_write(x, w, b, up=up, rank=rank, cta_group=2)
+        _, out, clean_pull = h.run_pull(peers, w_pull, b_pull, rank=rank, cta_group=2)
+        assert clean and clean_pull
+        results.append((torch.cat(slots, dim=1), out))
+    for got_pw, got_pull in results[1:]:
+        assert torch.equal(got_pw, results[0][0])
+        assert torch.equal(got_pull, results[0][1])
+
+
 def test_pull_kernel_is_bit_stable_across_many_launches_under_contention() -> None:
     """Every launch reuses the same monotonically increasing counters; a side
     stream keeps SMs busy so CTAs start at different times."""
