@@ -148,6 +148,17 @@ int pull_rows_for(int shard) {
   return rows;
 }
 
+// A shard row wider than one ticket is cut into equal column segments.
+void set_pull_geometry(mup::GemmParams& p, int rows) {
+  const int vec_per_row = p.shard / 8;
+  p.pull_rows = pull_rows_for(p.shard);
+  p.pull_segs = (vec_per_row + mup::kPullMaxVecs - 1) / mup::kPullMaxVecs;
+  if (p.pull_segs < 1) p.pull_segs = 1;
+  p.pull_seg_vecs = (vec_per_row + p.pull_segs - 1) / p.pull_segs;
+  const int groups = (rows + p.pull_rows - 1) / p.pull_rows;
+  p.total_tickets = groups * p.up * p.pull_segs;
+}
+
 int shape_rule(int64_t width, int up) {
   if (up != 2 && up != 4 && up != 8) return 1;
   if (width <= 0 || width % up) return 2;
@@ -887,9 +898,7 @@ int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k
     unsigned long long* ws = static_cast<unsigned long long*>(workspace);
     p.cursor = ws;
     p.ready = ws + 16;
-    p.pull_rows = pull_rows_for(p.shard);
-    const int groups = (rows + p.pull_rows - 1) / p.pull_rows;
-    p.total_tickets = groups * up;
+    set_pull_geometry(p, rows);
     for (int i = 0; i < up && rc == MUP_OK; ++i) {
       if (peer_arena_ptrs[i] == nullptr || reinterpret_cast<uintptr_t>(peer_arena_ptrs[i]) % 16)
         rc = fail(MUP_ERR_BAD_ARG, "peer arena pointer %d is null or not 16-byte aligned", i);
@@ -1099,9 +1108,7 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
   p.ready = dev->scratch + 16;
   p.epoch1 = 1;       // the scratch is cleared below, so every call is "the first launch"
   p.cursor_base = 0;
-  p.pull_rows = pull_rows_for(p.shard);
-  const int groups = (rows + p.pull_rows - 1) / p.pull_rows;
-  p.total_tickets = groups * up;
+  set_pull_geometry(p, rows);
   for (int i = 0; i < up; ++i) {
     if (peer_arena_ptrs[i] == nullptr || reinterpret_cast<uintptr_t>(peer_arena_ptrs[i]) % 16)
       return fail(MUP_ERR_BAD_ARG, "peer arena pointer %d is null or not 16-byte aligned", i);

@@ -51,7 +51,10 @@ constexpr int kEpiCols = 64;        // columns per epilogue sub-tile (128 bytes)
 constexpr int kEpiRows = 32;        // rows per epilogue warp
 constexpr int kEpiBufBytes = kEpiRows * kEpiCols * 2;  // 4096
 constexpr int kEpiBufs = 2;
-constexpr int kPullMaxVecs = 512;     // 16-byte vectors per pull ticket (one batch of peer loads per warp)
+#ifndef MUP_PULL_MAX_VECS
+#define MUP_PULL_MAX_VECS 512
+#endif
+constexpr int kPullMaxVecs = MUP_PULL_MAX_VECS;  // 16-byte vectors per pull ticket (one batch of peer loads per warp)
 constexpr int kPullUnroll = kPullMaxVecs / 32;
 constexpr int kPullWarps = 6;         // pull workers per CTA (warps 6 .. 6 + kPullWarps - 1)
 constexpr int kPullChunk = 8;         // tickets drawn per atomic
@@ -125,7 +128,9 @@ struct GemmParams {
   int peer_rows;
   int total_tickets;
   int pull_stride;                   // pull warps in the grid: distance between the tickets of a chunk
-  int pull_rows;                     // rows per pull ticket: a power of two <= 16 with pull_rows * shard / 8 <= 512
+  int pull_rows;                     // rows per pull ticket: a power of two <= 16 with pull_rows * shard / 8 <= kPullMaxVecs
+  int pull_segs;                     // column segments per shard row (> 1 only when one row exceeds a ticket; then pull_rows = 1)
+  int pull_seg_vecs;                 // 16-byte vectors per segment
   unsigned int flags;                // tuning switches (kFlag*)
   unsigned long long* trace;         // optional [grid][16] cycle counters (nullptr: off)
   SyncParams sync;                   // slot hand-off folded into this launch (flags[0] == nullptr: none)
@@ -149,12 +154,89 @@ constexpr int kTraceSlots = 16;
 constexpr unsigned int kFlagNoL2Hints = 8u;     // tuning: drop the L2 hints (W loads evict-last, output stores evict-first)
 constexpr unsigned int kFlagSplitCommit = 1u;  // G=2: one commit per CTA of the pair instead of one for both
 constexpr unsigned int kFlagSeparateIssue = 2u;  // tuning: poll, MMAs and commit as separate statements (the slower issue loop)
+constexpr unsigned int kFlagPullExtraFence = 16u;  // tuning: an explicit fence.acq_rel.gpu before every release of a ready count
 
 __device__ __forceinline__ void report_status(const GemmParams& p, volatile uint32_t* abort_flag,
                                               uint32_t code, uint32_t detail) {
   *abort_flag = 1u;
   if (p.status != nullptr) {
     *reinterpret_cast<volatile uint32_t*>(p.status) = (code << 24) | (detail & 0xFFFFFFu);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Pull tickets. Ticket t = (row group, source rank rotated from this rank,
+// column segment): pull_rows rows of one peer shard (or one segment of a single
+// row when a row alone exceeds a ticket), at most kPullMaxVecs 16-byte vectors.
+// ---------------------------------------------------------------------------
+struct PullTicket {
+  const __nv_bfloat16* src;
+  __nv_bfloat16* dst;
+  int nvec;
+  int panel;  // the 128-row panel the ticket belongs to
+};
+
+__device__ __forceinline__ PullTicket pull_ticket_geometry(const GemmParams& p, unsigned long long t) {
+  const int vec_per_row = p.shard >> 3;
+  const unsigned long long per_group = static_cast<unsigned long long>(p.up) * p.pull_segs;
+  const int grp = static_cast<int>(t / per_group);
+  const int within = static_cast<int>(t - static_cast<unsigned long long>(grp) * per_group);
+  const int seg = within % p.pull_segs;
+  int src_rank = within / p.pull_segs + p.rank + 1;
+  if (src_rank >= p.up) src_rank -= p.up;
+  const int r0 = grp * p.pull_rows;
+  int nrows = p.M - r0;
+  nrows = nrows > p.pull_rows ? p.pull_rows : nrows;
+  const int v0 = seg * p.pull_seg_vecs;
+  PullTicket k;
+  if (p.pull_segs > 1) {
+    k.nvec = vec_per_row - v0;
+    k.nvec = k.nvec > p.pull_seg_vecs ? p.pull_seg_vecs : k.nvec;
+  } else {
+    k.nvec = nrows * vec_per_row;  // <= kPullMaxVecs
+  }
+  k.src = p.peers[src_rank] + (static_cast<size_t>(p.rank) * p.peer_rows + r0) * static_cast<size_t>(p.shard) + v0 * 8;
+  k.dst = p.dy + static_cast<size_t>(r0) * p.K + static_cast<size_t>(src_rank) * p.shard + v0 * 8;
+  k.panel = grp / (kBlockM / p.pull_rows);
+  return k;
+}
+
+__device__ __forceinline__ void pull_ticket_load(const GemmParams& p, const PullTicket& k, int lane,
+                                                 uint4 (&regs)[kPullUnroll]) {
+  const int vec_per_row = p.shard >> 3;
+#pragma unroll
+  for (int u = 0; u < kPullUnroll; ++u) {
+    const int vidx = u * 32 + lane;
+    if (vidx < k.nvec) {
+      const int rr = vidx / vec_per_row;
+      const int cc = vidx - rr * vec_per_row;
+      regs[u] = ld_stream_v4(k.src + static_cast<size_t>(rr) * p.shard + cc * 8);
+    }
+  }
+}
+
+__device__ __forceinline__ void pull_ticket_store(const GemmParams& p, const PullTicket& k, int lane,
+                                                  const uint4 (&regs)[kPullUnroll]) {
+  const int vec_per_row = p.shard >> 3;
+#pragma unroll
+  for (int u = 0; u < kPullUnroll; ++u) {
+    const int vidx = u * 32 + lane;
+    if (vidx < k.nvec) {
+      const int rr = vidx / vec_per_row;
+      const int cc = vidx - rr * vec_per_row;
+      *reinterpret_cast<uint4*>(k.dst + static_cast<size_t>(rr) * p.K + cc * 8) = regs[u];
+    }
+  }
+}
+
+// Every lane's stores of the ticket precede this call (__syncwarp). The release
+// orders them (cumulatively, through the warp barrier) before the count; the
+// proxy fence orders them before the consumers' TMA reads.
+__device__ __forceinline__ void pull_ticket_publish(const GemmParams& p, int panel, int lane) {
+  if (lane == 0) {
+    fence_proxy_async_global();
+    if (p.flags & kFlagPullExtraFence) fence_acq_rel_gpu();
+    red_release_gpu_add_u64(reinterpret_cast<uint64_t*>(p.ready + panel), 1ull);
   }
 }
 
@@ -271,8 +353,8 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           const int groups_total = (p.M + p.pull_rows - 1) / p.pull_rows;
           int groups = groups_total - panel * groups_per_panel;
           groups = groups < 0 ? 0 : (groups > groups_per_panel ? groups_per_panel : groups);
-          const unsigned long long want =
-              p.epoch1 * static_cast<unsigned long long>(groups) * static_cast<unsigned long long>(p.up);
+          const unsigned long long want = p.epoch1 * static_cast<unsigned long long>(groups) *
+                                          static_cast<unsigned long long>(p.up) * static_cast<unsigned long long>(p.pull_segs);
           if (groups > 0) {
             const uint64_t t0 = globaltimer_ns();
             const long long gate_c0 = trace ? clock64() : 0;
@@ -624,27 +706,18 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   // the i-th run of consecutive tickets and panels complete in consumption
   // order. A ticket is published (proxy fence + release) while the next
   // ticket's loads are in flight.
+  // Measured and rejected: letting the idle epilogue warps copy tickets during
+  // start-up. More tickets in flight delayed the first panels (first gate open
+  // after 23 us instead of 17 us on two GPUs), and a second inlined copy of the
+  // ticket code in the kernel made this loop compile to something 1.7x slower
+  // per ticket even when the copy never ran; keep the ticket code in one place.
   if constexpr (MODE == MODE_PULL) {
     if (warp >= 6 && !misaligned) {
-      const int vec_per_row = p.shard >> 3;  // 16-byte vectors per shard row
-      const int groups_per_panel = kBlockM / p.pull_rows;
       const unsigned long long total = static_cast<unsigned long long>(p.total_tickets);
       const unsigned long long stride = static_cast<unsigned long long>(p.pull_stride);
       const unsigned long long block = stride * kPullChunk;  // tickets covered by `stride` chunks
       const unsigned long long chunks = (total + block - 1) / block * stride;
-      auto draw = [&]() -> unsigned long long {
-        unsigned long long c = 0;
-        if (lane == 0) c = atomicAdd(p.cursor, 1ull) - p.cursor_base + stride;
-        return __shfl_sync(0xffffffffu, c, 0);
-      };
-      auto publish = [&](int panel) {
-        // every lane's stores of that ticket precede this point (__syncwarp below)
-        if (lane == 0) {
-          fence_proxy_async_global();  // generic-proxy stores before the consumers' TMA (async-proxy) loads
-          fence_acq_rel_gpu();
-          red_release_gpu_add_u64(reinterpret_cast<uint64_t*>(p.ready + panel), 1ull);
-        }
-      };
+      auto publish = [&](int panel) { pull_ticket_publish(p, panel, lane); };
       // The peers' staged shards are handed off by the tail of their staging copy.
       {
         const bool handed = sync_wait_warp(p.sync, lane);
@@ -657,45 +730,23 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       // critical path of the first panels); the cursor hands out the rest.
       unsigned long long c = static_cast<unsigned long long>(blockIdx.x) * kPullWarps + (warp - 6);
       while (c < chunks && *abort_flag == 0u) {
-        const unsigned long long c_next = draw();
+        // Draw the next chunk now but read the result only after this chunk: at
+        // kernel start every pull warp of the grid hits the cursor at once and the
+        // same-address atomics take ~8 ns each, up to 7 us for the last warp.
+        unsigned long long drawn = 0;
+        if (lane == 0) drawn = atomicAdd(p.cursor, 1ull);
         const unsigned long long t_first = (c / stride) * block + (c % stride);
         for (int i = 0; i < kPullChunk; ++i) {
           const unsigned long long t = t_first + static_cast<unsigned long long>(i) * stride;
           if (t >= total) break;
-          const int grp = static_cast<int>(t / static_cast<unsigned long long>(p.up));
-          int src_rank = static_cast<int>(t - static_cast<unsigned long long>(grp) * p.up) + p.rank + 1;
-          if (src_rank >= p.up) src_rank -= p.up;
-          const int r0 = grp * p.pull_rows;
-          int nrows = p.M - r0;
-          nrows = nrows > p.pull_rows ? p.pull_rows : nrows;
-          const int nvec = nrows * vec_per_row;  // <= kPullMaxVecs
-          const __nv_bfloat16* src =
-              p.peers[src_rank] +
-              (static_cast<size_t>(p.rank) * p.peer_rows + r0) * static_cast<size_t>(p.shard);
-          __nv_bfloat16* dst = p.dy + static_cast<size_t>(r0) * p.K +
-                               static_cast<size_t>(src_rank) * p.shard;
+          const PullTicket k = pull_ticket_geometry(p, t);
+          const int panel = k.panel;
           uint4 regs[kPullUnroll];
-#pragma unroll
-          for (int u = 0; u < kPullUnroll; ++u) {
-            const int vidx = u * 32 + lane;
-            if (vidx < nvec) {
-              const int rr = vidx / vec_per_row;
-              const int cc = vidx - rr * vec_per_row;
-              regs[u] = ld_stream_v4(src + static_cast<size_t>(rr) * p.shard + cc * 8);
-            }
-          }
+          pull_ticket_load(p, k, lane, regs);
           if (pending_panel >= 0) publish(pending_panel);
-#pragma unroll
-          for (int u = 0; u < kPullUnroll; ++u) {
-            const int vidx = u * 32 + lane;
-            if (vidx < nvec) {
-              const int rr = vidx / vec_per_row;
-              const int cc = vidx - rr * vec_per_row;
-              *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rr) * p.K + cc * 8) = regs[u];
-            }
-          }
+          pull_ticket_store(p, k, lane, regs);
           __syncwarp();
-          pending_panel = grp / groups_per_panel;
+          pending_panel = panel;
           if (tickets_done < 2) {
             // start-up: the first panels gate every CTA, publish them at once
             publish(pending_panel);
@@ -703,7 +754,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
           ++tickets_done;
         }
-        c = c_next;
+        c = __shfl_sync(0xffffffffu, drawn, 0) - p.cursor_base + stride;
       }
       if (pending_panel >= 0) publish(pending_panel);
       // This warp will not read a peer arena again: once every pull warp of the

@@ -40,6 +40,8 @@ PULL_SHAPES = [
     (4096, 5120, 5120, 4, 0),
     (4096, 5120, 5120, 2, 1),
     (16384, 8192, 8192, 8, 4),     # Llama-3-70B O projection
+    (256, 256, 16384, 2, 1),       # a shard row (16 KB) wider than one pull ticket: two column segments
+    (130, 512, 12288, 2, 0),       # 12 KB shard rows, two segments of 6 KB, ragged M
 ]
 
 
@@ -115,7 +117,8 @@ def test_pull_kernel(rows, n, k, up, rank, cta_group) -> None:
         else:
             ref = F.linear(want_dy, w, b)
             if not torch.equal(out, ref):
-                assert rows < 256
+                # only outputs too small to fill the GPU, where cuBLAS splits K
+                assert rows < 256 or rows * n <= 256 * 512
                 assert h.ulp_distance(out, ref) <= 1
 
 
