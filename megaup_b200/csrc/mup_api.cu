@@ -235,6 +235,24 @@ int configure_kernel(int* max_clusters) {
   return MUP_OK;
 }
 
+// Programmatic dependent launch: every kernel of this library is launched with
+// the programmatic-serialization attribute, lets its successor be scheduled at
+// once (griddepcontrol.launch_dependents at entry) and waits for its
+// predecessor with griddepcontrol.wait before it touches global memory, so the
+// launch latency and the set-up of a kernel (barrier init, TMEM allocation,
+// cluster sync) hide behind the tail of the kernel before. A kernel launched
+// by someone else after these waits for their full completion as usual.
+// Measured on 2 B200s: peer-write call 171.8 -> 170.5 us, pull call 190.4 ->
+// 187.9 us, both back to back 367.3 -> 365.3 us. MEGA_UP_PDL=0 turns it off.
+bool pdl_enabled() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* env = getenv("MEGA_UP_PDL");
+    cached = (env != nullptr && atoi(env) == 0) ? 0 : 1;
+  }
+  return cached == 1;
+}
+
 template <int G, int MODE>
 int launch_kernel(const mup::GemmParams& params, int grid, cudaStream_t stream) {
   auto kernel = mup::fused_exchange_gemm_kernel<G, MODE>;
@@ -244,15 +262,40 @@ int launch_kernel(const mup::GemmParams& params, int grid, cudaStream_t stream) 
   cfg.blockDim = dim3(mup::kernel_threads(MODE), 1, 1);
   cfg.dynamicSmemBytes = mup::GemmCfg<G>::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = G;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = (G == 2) ? 1 : 0;
+  cudaLaunchAttribute attrs[2];
+  int n = 0;
+  if (G == 2) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = G;
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
   MUP_CUDA(cudaLaunchKernelEx(&cfg, kernel, params));
   return MUP_OK;
+}
+
+// Launch of the small kernels (barrier, layout copies), with the same attribute.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_small(void (*kernel)(KArgs...), int grid, int block, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // Shared plan state of the two operators.
@@ -422,6 +465,8 @@ struct FlagParams {
 };
 
 __global__ void flag_barrier_kernel(FlagParams fp) {
+  mup::grid_dep_launch();
+  mup::grid_dep_wait();  // the flag vouches for everything earlier kernels of the stream wrote
   const int peer = threadIdx.x;
   if (peer >= fp.up) return;
   // Everything this GPU wrote before the barrier (including stores to peer
@@ -449,6 +494,8 @@ __global__ void flag_barrier_kernel(FlagParams fp) {
 // dst row i <- src row index[i]; rows are `vecs` 16-byte vectors wide.
 __global__ void gather_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
                                    const int64_t* __restrict__ index, int64_t rows, int64_t vecs) {
+  mup::grid_dep_launch();
+  mup::grid_dep_wait();
   const int64_t total = rows * vecs;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -463,6 +510,8 @@ __global__ void gather_rows_kernel(uint4* __restrict__ dst, const uint4* __restr
 // Source-major [up, batch, seq] <-> batch-major [batch, up, seq] regroup of rows.
 __global__ void regroup_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int up,
                                     int batch, int64_t seq, int64_t vecs, int to_batch_major) {
+  mup::grid_dep_launch();
+  mup::grid_dep_wait();
   const int64_t rows = static_cast<int64_t>(up) * batch * seq;
   const int64_t total = rows * vecs;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -764,8 +813,7 @@ int mup_flag_barrier(void* const* peer_flags, int up, int rank, uint32_t epoch,
   fp.epoch = epoch;
   fp.up = up;
   fp.rank = rank;
-  flag_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(fp);
-  MUP_CUDA(cudaGetLastError());
+  MUP_CUDA(launch_small(flag_barrier_kernel, 1, 32, static_cast<cudaStream_t>(stream), fp));
   return MUP_OK;
 }
 
@@ -1151,9 +1199,8 @@ int mup_gather_rows(void* dst, const void* src, const int64_t* index, int64_t ro
   if (reinterpret_cast<uintptr_t>(dst) % 16 || reinterpret_cast<uintptr_t>(src) % 16)
     return fail(MUP_ERR_BAD_ARG, "gather buffers must be 16-byte aligned");
   const int64_t vecs = row_elems / 8;
-  gather_rows_kernel<<<copy_grid(rows * vecs), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<uint4*>(dst), static_cast<const uint4*>(src), index, rows, vecs);
-  MUP_CUDA(cudaGetLastError());
+  MUP_CUDA(launch_small(gather_rows_kernel, copy_grid(rows * vecs), 256, static_cast<cudaStream_t>(stream),
+                        static_cast<uint4*>(dst), static_cast<const uint4*>(src), index, rows, vecs));
   return MUP_OK;
 }
 
@@ -1203,10 +1250,9 @@ int mup_regroup_rows(void* dst, const void* src, int up, int batch, int64_t seq,
     return fail(MUP_ERR_BAD_ARG, "regroup buffers must be 16-byte aligned");
   const int64_t vecs = row_elems / 8;
   const int64_t total = static_cast<int64_t>(up) * batch * seq * vecs;
-  regroup_rows_kernel<<<copy_grid(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<uint4*>(dst), static_cast<const uint4*>(src), up, batch, seq, vecs,
-      to_batch_major);
-  MUP_CUDA(cudaGetLastError());
+  MUP_CUDA(launch_small(regroup_rows_kernel, copy_grid(total), 256, static_cast<cudaStream_t>(stream),
+                        static_cast<uint4*>(dst), static_cast<const uint4*>(src), up, batch, seq, vecs,
+                        to_batch_major));
   return MUP_OK;
 }
 

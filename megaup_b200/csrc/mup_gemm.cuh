@@ -291,6 +291,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + Cfg::kOffAbort);
   const uint64_t timeout_ns = p.timeout_ns;
   unsigned long long* trace = (p.trace != nullptr) ? p.trace + static_cast<size_t>(blockIdx.x) * kTraceSlots : nullptr;
+  grid_dep_launch();  // the next kernel may be scheduled now; it waits for this one in its own grid_dep_wait
   if (trace != nullptr && threadIdx.x == 0) {
     trace[kTraceStart] = clock64();
     trace[kTraceNsStart] = globaltimer_ns();
@@ -327,6 +328,9 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const bool misaligned = (*abort_flag != 0u);
+  // Everything above touched only this CTA's shared memory and TMEM; from here
+  // on the kernel reads what earlier kernels of the stream wrote.
+  grid_dep_wait();
 
   // ------------------------------------------------------------ TMA producer
   if (warp == 0 && !misaligned) {

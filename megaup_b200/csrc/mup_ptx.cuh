@@ -104,6 +104,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Programmatic dependent launch. `grid_dep_launch` lets the next kernel of the
+// stream be scheduled while this one still runs (it then sits in its own
+// `grid_dep_wait`); `grid_dep_wait` returns once the previous kernel has
+// completed and its memory operations are visible. Both are no-ops for a
+// kernel launched without the programmatic-serialization attribute.
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Non-blocking test of a phase (try_wait may suspend the thread for a while).
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
