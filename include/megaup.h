@@ -169,6 +169,12 @@ int mup_peer_write_plan_destroy(mup_peer_write_plan *plan);
 
 /* ---- head-shard pull GEMM --------------------------------------------------- */
 
+/* Shape of a pull ticket for shard rows of `shard_elems` BF16 (host arithmetic
+ * only): `*rows` rows of one peer shard per ticket, or, when a single row
+ * exceeds a ticket, `*segments` equal column segments of one row. Describes what
+ * the reference tabulates in _vector_pull_rows_per_ticket / _pull_column_chunks
+ * (headshard_pull_gemm.py:166-198) for its own kernel. */
+int mup_pull_ticket_shape(int shard_elems, int *rows, int *segments);
 /* Bytes of zero-initialised device workspace a pull plan for `rows` needs. */
 uint64_t mup_pull_workspace_bytes(int rows);
 

@@ -92,6 +92,7 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
     "mup_pull_launch": (c_int, (c_void_p, c_void_p)),
     "mup_pull_launch_synced": (c_int, (c_void_p, c_void_p, POINTER(MupSync))),
     "mup_pull_plan_reset": (c_int, (c_void_p, c_void_p)),
+    "mup_pull_ticket_shape": (c_int, (c_int, POINTER(c_int), POINTER(c_int))),
     "mup_pull_plan_info": (
         c_int,
         (c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_uint64), POINTER(c_int), POINTER(c_int)),

@@ -907,6 +907,18 @@ int mup_peer_write_plan_destroy(mup_peer_write_plan* plan) {
 
 // ---------------------------------------------------------------- pull
 
+int mup_pull_ticket_shape(int shard_elems, int* rows, int* segments) {
+  if (shard_elems <= 0 || shard_elems % 8) return fail(MUP_ERR_BAD_ARG, "shard must be a positive multiple of 8 elements");
+  mup::GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.shard = shard_elems;
+  p.up = 1;
+  set_pull_geometry(p, 1);
+  if (rows != nullptr) *rows = p.pull_rows;
+  if (segments != nullptr) *segments = p.pull_segs;
+  return MUP_OK;
+}
+
 uint64_t mup_pull_workspace_bytes(int rows) {
   if (rows <= 0) return 0;
   const uint64_t panels = (static_cast<uint64_t>(rows) + mup::kBlockM - 1) / mup::kBlockM;

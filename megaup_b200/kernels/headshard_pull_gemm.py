@@ -23,6 +23,52 @@ from .. import _native
 
 IMPLEMENTATION_REVISION = "megaup-b200-cuda-r1"
 TILE_N = 256
+# BF16 elements one pull warp keeps in flight: a ticket is at most 512 16-byte vectors.
+PULL_MAX_ELEMENTS_IN_FLIGHT = 512 * 8
+WARP_SIZE = 32
+
+
+def _ticket_shape(shard_k: int) -> tuple[int, int]:
+    rows, segments = ctypes.c_int(), ctypes.c_int()
+    try:
+        _native.call("mup_pull_ticket_shape", int(shard_k), ctypes.byref(rows), ctypes.byref(segments))
+    except _native.NativeError as error:
+        raise ValueError(str(error)) from None
+    return rows.value, segments.value
+
+
+def _select_pull_elements_per_lane(shard_k: int) -> int:
+    """BF16 elements per lane and load: this kernel always pulls with 16-byte
+    vectors (the reference chooses 4, 8 or 16 elements by shard width,
+    headshard_pull_gemm.py:137-142)."""
+
+    _ticket_shape(shard_k)  # validates the shard width
+    return 8
+
+
+def _vector_pull_rows_per_ticket(pull_rows_per_ticket: int, shard_k: int) -> int:
+    """Rows of one peer shard per ticket: the largest power of two, at most 16
+    and at most ``pull_rows_per_ticket``, whose rows fit
+    ``PULL_MAX_ELEMENTS_IN_FLIGHT`` (reference table: headshard_pull_gemm.py:166-182)."""
+
+    rows, _ = _ticket_shape(shard_k)
+    limit = max(1, int(pull_rows_per_ticket))
+    while rows > limit:
+        rows //= 2
+    return rows
+
+
+def _pull_column_chunks(shard_k: int, rows_in_flight: int) -> int:
+    """Equal column segments a shard row is cut into so that ``rows_in_flight``
+    rows of one segment fit a ticket (reference: headshard_pull_gemm.py:185-198).
+    The kernel itself only cuts rows that exceed a ticket on their own."""
+
+    _, segments = _ticket_shape(shard_k)
+    rows = max(1, int(rows_in_flight))
+    chunks = max(segments, -(-rows * shard_k // PULL_MAX_ELEMENTS_IN_FLIGHT))
+    while shard_k % chunks or (shard_k // chunks) % 8:
+        chunks += 1
+    return chunks
 
 
 class CompiledHeadShardPullGemm:
@@ -56,6 +102,14 @@ class CompiledHeadShardPullGemm:
         self.grid_ctas = grid.value
         self.cta_group = group.value
         self.smem_bytes = smem.value
+        # descriptors the reference's compiled object carries (run_pull_gemm_contention.py:225-254)
+        stage_bytes = 128 * 64 * 2 + (self.tile_n // self.cta_group) * 64 * 2
+        self.num_ab_stages = min(8, 196608 // stage_bytes)
+        self.num_c_stages = 2
+        self.enable_bulk_pull = False
+
+    def describe_pull(self, shard_k: int) -> None:
+        self.pull_rows_per_ticket, self.pull_col_chunks = _ticket_shape(shard_k)
 
     def reset_workspace(self, stream: torch.cuda.Stream | None = None) -> None:
         """Zero the counters on ``stream`` and restart the launch ordinal."""
@@ -159,6 +213,8 @@ def compile_headshard_pull_gemm(
         dy.data_ptr(), out.data_ptr(), workspace.data_ptr(), int(cta_group),
         status_address or None, int(timeout_ns),
     )
-    return CompiledHeadShardPullGemm(
+    compiled = CompiledHeadShardPullGemm(
         plan, workspace, (weight, bias, out, dy), workspace_epochs, rows, int(rank), int(up)
     )
+    compiled.describe_pull(k // int(up))
+    return compiled

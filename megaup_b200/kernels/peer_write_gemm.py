@@ -84,9 +84,11 @@ class PeerWriteLaunch:
         self.smem_bytes = smem.value
         self._out_spans = tuple(_span(out) for out in peer_outs)
 
-    def __call__(
-        self, a: Tensor, sync: "_native.MupSync | None" = None, stream_handle: int | None = None
-    ) -> None:
+    def check(self, a: Tensor) -> Tensor:
+        """The per-call contract on ``A`` (reference: PeerWriteLaunch.check,
+        peer_write_gemm.py:2660-2675): BF16, the bound shape, contiguous, on the
+        weight's device, not overlapping an output slot. Returns the 2-D view."""
+
         a = _as_2d(a, "A")
         if tuple(a.shape) != (self.rows, self.in_features):
             raise ValueError(
@@ -97,6 +99,12 @@ class PeerWriteLaunch:
         for start, stop in self._out_spans:
             if a_start < stop and start < a_stop:
                 raise ValueError("A overlaps an output slot")
+        return a
+
+    def __call__(
+        self, a: Tensor, sync: "_native.MupSync | None" = None, stream_handle: int | None = None
+    ) -> None:
+        a = self.check(a)
         stream = (
             stream_handle if stream_handle is not None else torch.cuda.current_stream(a.device).cuda_stream
         )
@@ -176,3 +184,29 @@ def make_peer_write_launch(
         status_address or None, int(timeout_ns),
     )
     return PeerWriteLaunch(plan, weight, bias, outs, rows, int(local_rank))
+
+
+def prepare_peer_write(
+    A: Tensor,
+    B: Tensor,
+    D: object,
+    PeerOuts: Sequence[Tensor],
+    *,
+    bias: Tensor | None = None,
+    local_rank: int = 0,
+    **tile_options: object,
+):
+    """Bind a peer-write launch to one ``A``: returns a callable without
+    arguments (reference: peer_write_gemm.py:2933-2980). The reference's tile and
+    scheduler keywords are accepted and ignored: this kernel has one tile shape."""
+
+    from functools import partial
+
+    if not isinstance(A, Tensor):
+        raise TypeError("peer_write requires a BF16 A tensor")
+    del D, tile_options
+    launch = make_peer_write_launch(
+        B, None, PeerOuts, a_shape=tuple(A.shape), bias=bias, local_rank=local_rank
+    )
+    launch.check(A)
+    return partial(launch, A)

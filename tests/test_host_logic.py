@@ -283,3 +283,29 @@ def test_mega_up_alias_package_resolves_to_this_implementation() -> None:
         "MegaUPRuntime", "DEFAULT_MAX_ROWS", "SUPPORTED_UP_DEGREES",
     ):
         assert hasattr(alias, name), name
+
+
+def test_secondary_surface_of_the_kernel_modules() -> None:
+    """Names the reference's own tests and benchmarks import from its kernel modules
+    (tests/test_shapes.py:50, benchmarks/bench_bshd.py:873, tests/run_pull_gemm_contention.py:225-254),
+    describing this kernel: 16-byte lanes, tickets of at most 512 vectors."""
+
+    import importlib
+
+    pw = importlib.import_module("mega_up.kernels.peer_write_gemm")
+    pull = importlib.import_module("mega_up.kernels.headshard_pull_gemm")
+    assert pw.PEER_TILE_N == 256 and isinstance(pw.IMPLEMENTATION_REVISION, str)
+    assert isinstance(pull.IMPLEMENTATION_REVISION, str)
+    with pytest.raises(TypeError, match="BF16 A tensor"):
+        pw.prepare_peer_write(None, None, None, ())
+    assert pull.PULL_MAX_ELEMENTS_IN_FLIGHT == 4096
+    # (shard width, rows per ticket, column segments of one row)
+    for shard, rows, segments in ((128, 16, 1), (640, 4, 1), (1024, 4, 1), (1280, 2, 1), (2560, 1, 1), (4096, 1, 1), (6144, 1, 2), (8192, 1, 2)):
+        assert pull._select_pull_elements_per_lane(shard) == 8
+        assert pull._vector_pull_rows_per_ticket(16, shard) == rows
+        assert pull._vector_pull_rows_per_ticket(2, shard) == min(rows, 2)
+        assert pull._pull_column_chunks(shard, 1) == segments
+        assert rows * shard // segments <= pull.PULL_MAX_ELEMENTS_IN_FLIGHT
+    assert pull._pull_column_chunks(640, 8) == 2  # eight rows of 640 need two segments of 320
+    with pytest.raises(ValueError):
+        pull._select_pull_elements_per_lane(100)
