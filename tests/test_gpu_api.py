@@ -93,7 +93,7 @@ def test_api_matches_the_reference_unfused_path(name: str) -> None:
 
 @pytest.mark.parametrize("up", [2, 4, 8])
 def test_wan_q_and_o_projection_bshd(up: int) -> None:
-    """BASELINE configuration 2: W[5120,5120] + bias, B=1, S_local=4096, H=40, D=128."""
+    """Wan2.1-14B-shaped Q/O projection: W[5120,5120] + bias, B=1, S_local=4096, H=40, D=128."""
 
     seq, heads, dim, hidden = 4096, 40, 128, 5120
     runtimes = _group(up, hidden, seq)
@@ -136,7 +136,7 @@ def test_wan_q_and_o_projection_bshd(up: int) -> None:
 
 
 def test_llama8b_fused_qkv_sbhd_peer_write() -> None:
-    """BASELINE configuration 3 at U=8: W[6144,4096], no bias, SBHD, S_local=8192, B=1."""
+    """Llama-3-8B-shaped fused QKV at U=8: W[6144,4096], no bias, SBHD, S_local=8192, B=1."""
 
     up, seq, heads, dim = 8, 8192, 32, 128
     runtimes = _group(up, 6144, seq)
@@ -155,7 +155,7 @@ def test_llama8b_fused_qkv_sbhd_peer_write() -> None:
 
 
 def test_llama70b_o_projection_thd_layout_pull() -> None:
-    """BASELINE configuration 4: W[8192,8192], U=8, T_local=16384 of seeded
+    """Llama-3-70B-shaped O projection: W[8192,8192], U=8, T_local=16384 of seeded
     variable-length samples (512..4096, last truncated), THDLayout row gather."""
 
     up, tokens, heads, dim = 8, 16384, 64, 128
@@ -190,7 +190,7 @@ def test_llama70b_o_projection_thd_layout_pull() -> None:
 
 
 def test_shape_edge_sweep() -> None:
-    """BASELINE configuration 5: (a) 2304 wide, U=2, B=4 strided copies; (b) 2048, D=64,
+    """Edge shapes: (a) 2304 wide, U=2, B=4 strided copies; (b) 2048, D=64,
     U=8; (c) W[1024,4096], U=8, 64 rows (cuBLAS split-K tolerance case)."""
 
     cases = [
