@@ -16,7 +16,14 @@
 //
 // The FP32 accumulator of an output element is a single TMEM cell that
 // receives the K products in ascending order, 16 at a time; bias is added in
-// FP32 and the sum is rounded to BF16 once.
+// FP32 and the sum is rounded to BF16 once. Nothing about the schedule (tile
+// width, which SM runs which tile, the half-width items of a partly filled
+// last wave) changes that order, so every configuration gives the same bits.
+//
+// Schedule: persistent CTAs, static round-robin over work items in N-fastest
+// order (peer-write: each rank starts at its own column block). The kernel
+// is launched with programmatic stream serialization: it lets its successor
+// be scheduled at entry and waits for its predecessor after its own set-up.
 //
 // Warp roles (192 threads, 384 in pull mode):
 //   warp 0      TMA producer (one elected lane)
