@@ -106,77 +106,157 @@ class ClockSampler:
 # --------------------------------------------------------------------------- CPU legs
 
 
-def cpu_step_rate(budget_s: float, steps: int | None = None, warmup: int = 1) -> dict:
-    """Time the unfused CPU path (oracle/unfused_torch.py) on the host cores; the
-    sample shrinks to a slice of the rows when a full step is too slow."""
+def host_cores() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_step_rate(budget_s: float, steps: int | None, warmup: int, up: int, group, world: int, threads: int) -> dict:
+    """Time the unfused path on the host cores: ``F.linear`` + permute +
+    ``all_to_all_single`` (peer-write direction) and ``all_to_all_single`` +
+    permute + ``F.linear`` (pull direction), the reference's own baseline
+    functions when they are installed. ``group`` is a gloo group of ``world``
+    processes that all call this function; every rank runs ``threads`` torch
+    threads. A step works on a slice of the 4096 rows when a full step would be
+    too slow; the rate is per FLOP, so the slice does not bias it."""
 
     import torch
+    import torch.distributed as dist
 
-    from oracle.unfused_torch import UnfusedRank
+    from oracle.unfused_torch import reference_baselines
 
-    rows = TOKENS
-    rank = UnfusedRank(rows, HIDDEN, 8)
-    start = time.perf_counter()
-    rank.step()
-    first = time.perf_counter() - start
-    if first > budget_s / 4 and rows > 256:
-        rows = max(256, int(rows * (budget_s / 8) / first) // 128 * 128)
-        rank = UnfusedRank(rows, HIDDEN, 8)
-        rank.step()
-    for _ in range(max(0, warmup - 1)):
-        rank.step()
-    times = []
+    torch.set_num_threads(threads)
+    baseline_peer_write, baseline_pull_gemm, kind = reference_baselines()
+    rank = dist.get_rank(group)
+    gen = torch.Generator().manual_seed(1234)
+    scale = HIDDEN ** -0.5
+    w_q = (torch.randn(HIDDEN, HIDDEN, generator=gen) * scale).to(torch.bfloat16)
+    w_o = (torch.randn(HIDDEN, HIDDEN, generator=gen) * scale).to(torch.bfloat16)
+    b_q = (torch.randn(HIDDEN, generator=gen) * 0.02).to(torch.bfloat16)
+    b_o = (torch.randn(HIDDEN, generator=gen) * 0.02).to(torch.bfloat16)
+    rank_gen = torch.Generator().manual_seed(5678 + rank)
+
+    def make(rows: int):
+        x = torch.randn(1, rows, HEADS, HEAD_DIM, generator=rank_gen).to(torch.bfloat16)
+        head_x = torch.randn(1, up * rows, HEADS // up, HEAD_DIM, generator=rank_gen).to(torch.bfloat16)
+        return x, head_x
+
+    def step(x, head_x) -> None:
+        baseline_peer_write(x, w_q, b_q, up=up, group=group)
+        baseline_pull_gemm(head_x, w_o, b_o, up=up, group=group)
+
+    def agree_max(value: float) -> float:
+        t = torch.tensor([value], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return float(t.item())
+
+    rows = 256
+    x, head_x = make(rows)
+    step(x, head_x)  # first touch: thread pools, gloo buffers
+    dist.barrier(group)
     begin = time.perf_counter()
+    step(x, head_x)
+    probe = agree_max(time.perf_counter() - begin)
+    # a step of about a quarter of a second, at most the full 4096 rows
+    target = max(0.05, min(0.25, budget_s / 40))
+    rows = int(min(TOKENS, max(256, rows * target / max(probe, 1e-4)))) // 128 * 128
+    x, head_x = make(rows)
+    for _ in range(max(1, warmup)):
+        step(x, head_x)
+    times: list[float] = []
+    overall = time.perf_counter()
     while True:
-        start = time.perf_counter()
-        rank.step()
-        times.append(time.perf_counter() - start)
-        if steps is not None and len(times) >= steps:
-            break
-        if steps is None and (time.perf_counter() - begin > budget_s or len(times) >= 50):
+        dist.barrier(group)
+        begin = time.perf_counter()
+        step(x, head_x)
+        times.append(agree_max(time.perf_counter() - begin))
+        done = len(times) >= steps if steps is not None else (
+            agree_max(time.perf_counter() - overall) > budget_s or len(times) >= 50
+        )
+        if done:
             break
     seconds = statistics.median(times)
+    flops_per_rank = 2 * 2.0 * rows * HIDDEN * HIDDEN
     return {
-        "value": rank.flops_per_step / seconds / 1e12,
+        "value": world * flops_per_rank / seconds / 1e12,
         "unit": "TFLOP/s",
-        "cores": torch.get_num_threads(),
-        "kind": "port",
+        "cores": threads * world,
+        "kind": kind,
         "sample": (
-            f"{len(times)} steps of one rank's unfused F.linear + permute + all-to-all copies, "
-            f"{rows} of {TOKENS} rows, W[{HIDDEN},{HIDDEN}] BF16, torch CPU"
+            f"{len(times)} steps of the unfused F.linear + permute + gloo all_to_all_single path "
+            f"(both directions), {rows} of {TOKENS} rows per rank, W[{HIDDEN},{HIDDEN}] BF16, "
+            f"{world} process(es) x {threads} torch threads, UP={up}"
         ),
-        "ms_per_step": seconds * 1e3,
+        "ms_per_step": seconds * 1e3 * TOKENS / rows,
         "rows": rows,
+        "ms_per_sampled_step": seconds * 1e3,
     }
+
+
+def cpu_group(world: int):
+    """A gloo group for the CPU legs: the torchrun ranks, or this process alone."""
+
+    import torch.distributed as dist
+
+    if world > 1:
+        if not dist.is_initialized():
+            dist.init_process_group("gloo")
+        return dist.group.WORLD
+    if dist.is_initialized():
+        return dist.new_group(ranks=[dist.get_rank()], backend="gloo")
+    import tempfile
+
+    store = dist.FileStore(tempfile.mktemp(prefix="megaup_bench_"), 1)
+    dist.init_process_group("gloo", store=store, rank=0, world_size=1)
+    return dist.group.WORLD
 
 
 def run_reference_arm(args) -> None:
-    """The reference's own CPU implementation of the path (its unfused torch path),
-    all host threads, rank 0 only."""
+    """The reference's own CPU implementation of the path (its unfused torch path
+    under gloo) on the host cores. Under torchrun every rank runs with its share
+    of the cores and the ranks exchange with a real all_to_all_single (UP = N);
+    `value` is the whole-job rate like the GPU arm's. Alone (N = 1) one process
+    with all cores plays one rank of a UP = 8 group."""
 
-    if int(os.environ.get("RANK", "0")) != 0:
-        return
-    result = cpu_step_rate(budget_s=60.0, steps=args.steps, warmup=max(1, args.warmup))
-    line = {
-        "impl": "reference",
-        "metric": "fused_proj_a2a_tflops",
-        "value": result["value"],
-        "unit": "TFLOP/s",
-        "n_gpus": args.gpus,
-        "steps": args.steps,
-        "warmup": args.warmup,
-        "ms_per_step": result["ms_per_step"],
-        "higher_is_better": True,
-        "scaling": "weak",
-        "vs_baseline": None,
-        "dtype": "bf16",
-        "data": "synthetic",
-        "config": workload_config(max(args.gpus, 1)),
-        "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
-        "e2e": {"value": result["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
-    }
-    print(json.dumps(line), flush=True)
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    threads = max(1, host_cores() // world)
+    up = world if world > 1 else 8
+    group = cpu_group(world)
+    result = cpu_step_rate(
+        budget_s=60.0, steps=args.steps, warmup=max(1, args.warmup), up=up, group=group, world=world,
+        threads=threads,
+    )
+    if rank == 0:
+        line = {
+            "impl": "reference",
+            "metric": "fused_proj_a2a_tflops",
+            "value": result["value"],
+            "unit": "TFLOP/s",
+            "n_gpus": args.gpus,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": result["ms_per_step"],
+            "sampled_rows": result["rows"],
+            "ms_per_sampled_step": result["ms_per_sampled_step"],
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic",
+            "config": workload_config(max(args.gpus, 1)),
+            "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": result["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }
+        print(json.dumps(line), flush=True)
+    if dist.is_initialized():
+        dist.barrier(group)
+        dist.destroy_process_group()
 
 
 def workload_config(n_gpus: int) -> dict:
@@ -530,7 +610,9 @@ def main() -> None:
             "correctness_gate": "bit-exact vs cuBLAS + torch exchange",
         }
         if not distributed and not args.no_cpu_baseline:
-            cpu = cpu_step_rate(budget_s=15.0)
+            cpu = cpu_step_rate(
+                budget_s=15.0, steps=None, warmup=1, up=up, group=cpu_group(1), world=1, threads=host_cores()
+            )
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)
     if distributed:

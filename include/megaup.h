@@ -72,6 +72,21 @@ int mup_shape_rule(int64_t width, int up);
  * Replaces mega_up/kernels/peer_write_gemm.py:977-993 (peer_n_rotation). */
 int mup_peer_n_rotation(int rank, int up, int n_total, int tile_n);
 
+/* The work-item list the library would run for a problem, without touching a
+ * GPU (host arithmetic only): `slots` CTAs (cta_group 1) or CTA pairs
+ * (cta_group 0 or 2) that are resident at once run items i, i + slots, ... in
+ * list order. Item encoding: bits 0-13 row tile (128 * cta_group rows), bits
+ * 14-25 first column / 64, bits 26-28 columns / 64 - 1. Writes at most
+ * `capacity` items, the full count, the widest item in columns and the
+ * critical path the library's time model predicts (SM cycles). mode 0 =
+ * peer-write (each rank starts every row at its own column block), 1 = pull.
+ * Plays the part of the reference's tile scheduler parameters
+ * (mega_up/kernels/peer_write_gemm.py:775-781, headshard_pull_gemm.py:1227-1268),
+ * which it fixes at compile time. Any output pointer may be NULL. */
+int mup_schedule_preview(int mode, int rows, int n, int k, int up, int rank, int cta_group, int slots,
+                         uint32_t *items, int capacity, int *count, int *max_item_cols,
+                         double *model_cycles);
+
 /* ---- status word ---------------------------------------------------------- */
 
 /* One 64-byte block of pinned, device-mapped host memory. `host_ptr` is read
@@ -154,7 +169,8 @@ int mup_peer_write_launch(mup_peer_write_plan *plan, const void *a, void *stream
 int mup_peer_write_launch_synced(mup_peer_write_plan *plan, const void *a, void *stream,
                                  mup_sync *sync);
 /* Any output pointer may be NULL. tile_n is the width of an output tile the
- * library chose for this problem (128, 192 or 256 columns). */
+ * widest work item the library chose for this problem (64 .. 512 columns);
+ * n_rotation is the first column of the first item in 256-column blocks. */
 int mup_peer_write_plan_info(const mup_peer_write_plan *plan, int *grid_ctas, int *cta_group,
                              int *n_rotation, int *smem_bytes, int *tile_n);
 /* Cycle tracing (no counterpart in the reference, which has no built-in tracing):

@@ -7,10 +7,12 @@ CPU fallback. Loading fails loudly when the shared object is missing.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, c_char_p, c_int, c_int64, c_uint32, c_uint64, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libmegaup.so"
+# MEGAUP_LIBRARY names another build of the library (A/B comparisons of kernel variants).
+LIB_PATH = Path(os.environ.get("MEGAUP_LIBRARY") or Path(__file__).resolve().parent / "_lib" / "libmegaup.so")
 
 MUP_OK = 0
 ERROR_NAMES = {
@@ -55,6 +57,13 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
     "mup_device_supported": (c_int, (c_int, POINTER(c_int))),
     "mup_shape_rule": (c_int, (c_int64, c_int)),
     "mup_peer_n_rotation": (c_int, (c_int, c_int, c_int, c_int)),
+    "mup_schedule_preview": (
+        c_int,
+        (
+            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_uint32), c_int,
+            POINTER(c_int), POINTER(c_int), POINTER(ctypes.c_double),
+        ),
+    ),
     "mup_status_create": (c_int, (POINTER(POINTER(c_uint32)), POINTER(c_void_p))),
     "mup_status_destroy": (c_int, (POINTER(c_uint32),)),
     "mup_arena_create": (c_int, (c_int, c_uint64, POINTER(c_void_p))),

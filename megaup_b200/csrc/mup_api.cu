@@ -15,8 +15,10 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
 #include <mutex>
 #include <new>
+#include <vector>
 
 #include "../../include/megaup.h"
 #include "mup_gemm.cuh"
@@ -305,6 +307,12 @@ struct PlanCore {
   int cta_group = 1;
   int grid = 0;
   int smem_bytes = 0;
+  std::vector<uint32_t> host_items;  // the work-item list (host copy)
+  void* device_items = nullptr;      // the same list in device memory (owned)
+  double model_cycles = 0;           // critical path the time model predicts
+  ~PlanCore() {
+    if (device_items != nullptr) cudaFree(device_items);
+  }
 };
 
 int check_common(int device, int rows, int n, int k, int up, int rank, const void* weight,
@@ -327,53 +335,200 @@ int check_common(int device, int rows, int n, int k, int up, int rank, const voi
   return MUP_OK;
 }
 
-// Width of an output tile. Every SM reads (128 + tile_n / 2) operand rows per
-// tile_n output columns of its 128 rows (CTA pair), so the L2 -> SM traffic of
-// the whole GEMM is 1.68 GB at 256, 1.96 GB at 192 and 2.52 GB at 128 for the
-// 4096 x 5120 x 5120 problem. Measured, all three widths move ~11-12 TB/s and
-// take 149 / 162 / 206 us: below 256 the kernel is bound by that traffic, not
-// by the tensor pipe (in isolation, on resident operands, the issue sequence
-// keeps the pipe full at every width). A narrower tile therefore only pays off
-// when it removes whole waves; ties go to the widest tile.
-// MEGA_UP_TILE_N overrides the choice (tuning only).
-int choose_tile_n(int m_tiles, int n, int slots) {
-  if (const char* env = getenv("MEGA_UP_TILE_N")) {
-    const int forced = atoi(env);
-    if (forced == 128 || forced == 192 || forced == 256) return forced;
+// ---------------------------------------------------------------- schedule
+//
+// The output is cut into work items of 128*G rows by 64..512 columns; CTA
+// (pair) c runs items c, c + slots, ... of the list built here. The list is
+// chosen with a small time model of one K step of an item of `cols` columns:
+//
+//   tensor pipe   2 * cols cycles (128 x cols x 64 MACs per SM at 8192 FLOP/cycle)
+//   operand port  (128 + cols / G) rows * 128 bytes / port_bytes_per_cycle
+//
+// Measured on B200: 128-, 192- and 256-wide tiles all moved 11-12 TB/s from L2
+// to the SMs and took 206 / 162 / 149 us for 4096 x 5120 x 5120; inside the K
+// loop that is about 60 bytes per SM cycle, i.e. the port bounds every tile of
+// at most 256 columns while items of 384 columns and more (53 bytes per cycle
+// and less at full tensor rate) are bounded by the tensor pipe. For a number of rounds r the model spreads
+// r * slots items over the M tiles (rows of items differ by at most one item,
+// the items of a row by at most 64 columns), simulates the round-robin
+// assignment and keeps the list with the shortest critical path. Inside every
+// round after the first the items are then dealt so that the CTA (pair) with
+// the most work so far receives the cheapest item (`kNoItem` entries mark the
+// CTA pairs that sit out a partly filled last round).
+// Tuning overrides (environment): MEGA_UP_ITEM_UNITS=u forces items of u*64
+// columns, MEGA_UP_ROUNDS=r forces the number of rounds, MEGA_UP_BAND=b lists
+// the items of b consecutive M tiles column by column (peer-write only),
+// MEGA_UP_PORT_BPC sets the port term of the model.
+
+int env_int(const char* name, int fallback) {
+  const char* env = getenv(name);
+  return (env != nullptr && *env) ? atoi(env) : fallback;
+}
+
+struct Schedule {
+  std::vector<uint32_t> items;
+  int max_cols = 0;
+  double critical_cycles = 0;
+};
+
+double model_port_bytes_per_cycle() {
+  if (const char* env = getenv("MEGA_UP_PORT_BPC")) {
+    const double v = atof(env);
+    if (v > 1.0) return v;
   }
-  const int candidates[3] = {256, 192, 128};
-  int best = 256;
-  long long best_cost = -1;
-  for (int c = 0; c < 3; ++c) {
-    const int t = candidates[c];
-    const long long tiles = static_cast<long long>(m_tiles) * ((n + t - 1) / t);
-    const long long waves = (tiles + slots - 1) / slots;
-    const long long cost = waves;
-    if (best_cost < 0 || cost < best_cost) {
-      best_cost = cost;
-      best = t;
+  return 60.0;
+}
+
+double item_cycles(int units, int k_tiles, int g, double port_bpc) {
+  const double cols = units * static_cast<double>(mup::kUnit);
+  const double tensor = 2.0 * cols;
+  const double port = (mup::kBlockM + cols / g) * 128.0 / port_bpc;
+  // per item: the accumulator hand-over of its parts and the fill of the pipeline
+  const double fixed = units * mup::kUnit > mup::kBlockN ? 2500.0 : 1200.0;
+  return k_tiles * std::max(tensor, port) + fixed;
+}
+
+// Items of one M tile: `q` items covering `units` 64-column units, the first
+// units % q of them one unit wider; emitted from position `start` cyclically.
+void emit_row(std::vector<uint32_t>* out, int m_idx, int units, int q, int start) {
+  const int base = units / q, extra = units % q;
+  for (int j = 0; j < q; ++j) {
+    const int pos = (start + j) % q;
+    const int n0 = pos * base + std::min(pos, extra);
+    const int w = base + (pos < extra ? 1 : 0);
+    out->push_back(mup::encode_item(m_idx, n0, w));
+  }
+}
+
+double list_item_cycles(uint32_t e, int k_tiles, int g, double port_bpc) {
+  if (e == mup::kNoItem) return 0.0;
+  return item_cycles(static_cast<int>((e >> 26) & 0x7u) + 1, k_tiles, g, port_bpc);
+}
+
+double critical_path(const std::vector<uint32_t>& items, int slots, int k_tiles, int g, double port_bpc) {
+  std::vector<double> load(static_cast<size_t>(slots), 0.0);
+  for (size_t i = 0; i < items.size(); ++i) load[i % slots] += list_item_cycles(items[i], k_tiles, g, port_bpc);
+  return *std::max_element(load.begin(), load.end());
+}
+
+// Deal the items of every round after the first so that the slot with the most
+// work so far gets the cheapest item of the round; a partly filled last round
+// goes to the least loaded slots and the others get kNoItem. The first round
+// keeps list order (in pull mode its items are the first panels to arrive).
+void balance_rounds(std::vector<uint32_t>* items, int slots, int k_tiles, int g, double port_bpc) {
+  const size_t n = items->size();
+  if (n <= static_cast<size_t>(slots)) return;
+  std::vector<double> load(static_cast<size_t>(slots), 0.0);
+  std::vector<uint32_t> out;
+  out.reserve((n + slots - 1) / slots * slots);
+  for (size_t r0 = 0; r0 < n; r0 += slots) {
+    const size_t count = std::min(n - r0, static_cast<size_t>(slots));
+    std::vector<uint32_t> round(items->begin() + r0, items->begin() + r0 + count);
+    std::vector<uint32_t> placed(static_cast<size_t>(slots), mup::kNoItem);
+    if (r0 == 0) {
+      for (size_t i = 0; i < count; ++i) placed[i] = round[i];
+    } else {
+      std::vector<int> order(static_cast<size_t>(slots));
+      for (int c = 0; c < slots; ++c) order[static_cast<size_t>(c)] = c;
+      // most loaded slot first; ties keep the slot order
+      std::stable_sort(order.begin(), order.end(),
+                       [&](int a, int b) { return load[static_cast<size_t>(a)] > load[static_cast<size_t>(b)]; });
+      // cheapest item first; ties keep list order
+      std::stable_sort(round.begin(), round.end(), [&](uint32_t a, uint32_t b) {
+        return list_item_cycles(a, k_tiles, g, port_bpc) < list_item_cycles(b, k_tiles, g, port_bpc);
+      });
+      // with fewer items than slots the most loaded slots sit the round out
+      const size_t skip = static_cast<size_t>(slots) - count;
+      for (size_t i = 0; i < count; ++i) placed[static_cast<size_t>(order[skip + i])] = round[i];
     }
+    for (int c = 0; c < slots; ++c) {
+      load[static_cast<size_t>(c)] += list_item_cycles(placed[static_cast<size_t>(c)], k_tiles, g, port_bpc);
+      out.push_back(placed[static_cast<size_t>(c)]);
+    }
+  }
+  while (!out.empty() && out.back() == mup::kNoItem) out.pop_back();
+  items->swap(out);
+}
+
+// q_of_row[m] items for M tile m.
+Schedule build_list(const std::vector<int>& q_of_row, int units, int up, int rank, bool rotate, int band,
+                    int slots, int k_tiles, int g, double port_bpc) {
+  Schedule s;
+  const int m_tiles = static_cast<int>(q_of_row.size());
+  std::vector<std::vector<uint32_t>> rows(static_cast<size_t>(m_tiles));
+  for (int m = 0; m < m_tiles; ++m) {
+    const int q = q_of_row[m];
+    const int start = rotate ? ((rank * q + up - 1) / up) % q : 0;
+    emit_row(&rows[m], m, units, q, start);
+    s.max_cols = std::max(s.max_cols, ((units + q - 1) / q) * mup::kUnit);
+  }
+  if (band <= 1) {
+    for (int m = 0; m < m_tiles; ++m) s.items.insert(s.items.end(), rows[m].begin(), rows[m].end());
+  } else {
+    for (int m0 = 0; m0 < m_tiles; m0 += band) {
+      const int m1 = std::min(m_tiles, m0 + band);
+      size_t longest = 0;
+      for (int m = m0; m < m1; ++m) longest = std::max(longest, rows[m].size());
+      for (size_t j = 0; j < longest; ++j)
+        for (int m = m0; m < m1; ++m)
+          if (j < rows[m].size()) s.items.push_back(rows[m][j]);
+    }
+  }
+  if (env_int("MEGA_UP_BALANCE", 1) != 0) balance_rounds(&s.items, slots, k_tiles, g, port_bpc);
+  s.critical_cycles = critical_path(s.items, slots, k_tiles, g, port_bpc);
+  return s;
+}
+
+Schedule choose_schedule(int mode, int m_tiles, int n, int k_tiles, int up, int rank, int g, int slots) {
+  const int units = n / mup::kUnit;
+  const int max_units = mup::max_item_cols(g) / mup::kUnit;
+  const int q_min = (units + max_units - 1) / max_units;
+  const bool rotate = (mode == mup::MODE_PEER_WRITE);
+  const int band = rotate ? std::max(1, env_int("MEGA_UP_BAND", 1)) : 1;
+  const double port_bpc = model_port_bytes_per_cycle();
+  auto uniform = [&](int q) {
+    return build_list(std::vector<int>(static_cast<size_t>(m_tiles), q), units, up, rank, rotate, band, slots,
+                      k_tiles, g, port_bpc);
+  };
+  const int forced_units = env_int("MEGA_UP_ITEM_UNITS", 0);
+  if (forced_units >= 1 && forced_units <= max_units) {
+    return uniform(std::min(units, (units + forced_units - 1) / forced_units));
+  }
+  Schedule best;
+  bool have = false;
+  auto consider = [&](Schedule&& cand) {
+    if (!have || cand.critical_cycles < best.critical_cycles * 0.999 ||
+        (cand.critical_cycles <= best.critical_cycles * 1.001 && cand.items.size() < best.items.size())) {
+      best = std::move(cand);
+      have = true;
+    }
+  };
+  const int forced_rounds = env_int("MEGA_UP_ROUNDS", 0);
+  const long long min_items = static_cast<long long>(m_tiles) * q_min;
+  const int r_lo = forced_rounds > 0 ? forced_rounds : static_cast<int>((min_items + slots - 1) / slots);
+  const int r_hi = forced_rounds > 0 ? forced_rounds : r_lo + 3;
+  for (int r = std::max(1, r_lo); r <= r_hi; ++r) {
+    const long long target = static_cast<long long>(r) * slots;
+    long long q_lo = target / m_tiles;
+    long long rows_hi = target - q_lo * m_tiles;  // this many M tiles get one item more
+    if (q_lo < q_min) {
+      q_lo = q_min;
+      rows_hi = 0;
+    }
+    if (q_lo >= units) {
+      q_lo = units;
+      rows_hi = 0;
+    }
+    std::vector<int> q_of_row(static_cast<size_t>(m_tiles), static_cast<int>(q_lo));
+    for (long long m = 0; m < rows_hi; ++m) q_of_row[static_cast<size_t>(m)] = static_cast<int>(q_lo + 1);
+    consider(build_list(q_of_row, units, up, rank, rotate, band, slots, k_tiles, g, port_bpc));
+    if (rows_hi != 0) consider(uniform(static_cast<int>(q_lo)));
+    if (q_lo >= units) break;
   }
   return best;
 }
 
-// The last wave of the static schedule is usually partly filled (640 tiles on
-// 148 SMs: 4.32 waves). When it is at most half full, each of its tiles is run
-// as two half-width work items: about twice as many SMs work for half as
-// long. Half items read more of A per output column (the L2 -> SM traffic per
-// flop goes up by half), which is why only the tail is cut.
-// MEGA_UP_SPLIT_TAIL=0 turns the split off (tuning only).
-int choose_split_tiles(long long tiles, int slots, int tile_n) {
-  if (const char* env = getenv("MEGA_UP_SPLIT_TAIL")) {
-    if (atoi(env) == 0) return 0;
-  }
-  if (mup::kKSub != 1 || (tile_n != 256 && tile_n != 128)) return 0;
-  const long long rem = tiles % slots;
-  if (rem == 0 || 2 * rem > slots) return 0;
-  return static_cast<int>(rem);
-}
-
-// Fill the geometry shared by both modes and size the grid.
+// Fill the geometry shared by both modes, build the schedule and size the grid.
 template <int MODE>
 int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int rank,
                 int cta_group) {
@@ -387,37 +542,66 @@ int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int 
   p.K = k;
   p.up = up;
   p.rank = rank;
-  p.m_tiles = (rows + mup::kBlockM * g - 1) / (mup::kBlockM * g);
-  p.k_tiles = (k + mup::kStageK - 1) / mup::kStageK;
+  p.k_tiles = (k + mup::kBlockK - 1) / mup::kBlockK;
+  const int m_tiles = (rows + mup::kBlockM * g - 1) / (mup::kBlockM * g);
+  if (m_tiles > mup::kMaxItemMTiles || n / mup::kUnit > mup::kMaxItemNUnits)
+    return fail(MUP_ERR_UNSUPPORTED, "rows=%d or n=%d exceeds the schedule's range (%d row tiles, %d columns)", rows,
+                n, mup::kMaxItemMTiles, mup::kMaxItemNUnits * mup::kUnit);
   int max_clusters = 0;
+  int slots = info.sms;
   if (g == 1) {
     rc = configure_kernel<1, MODE>(&max_clusters);
     if (rc != MUP_OK) return rc;
-    p.tile_n = choose_tile_n(p.m_tiles, n, info.sms);
-    p.n_tiles = (n + p.tile_n - 1) / p.tile_n;
-    const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
-    p.split_tiles = choose_split_tiles(tiles, info.sms, p.tile_n);
-    const long long items = tiles + p.split_tiles;
-    core->grid = static_cast<int>(items < info.sms ? items : info.sms);
     core->smem_bytes = mup::GemmCfg<1>::kSmemBytes;
   } else {
     rc = configure_kernel<2, MODE>(&max_clusters);
     if (rc != MUP_OK) return rc;
     if (max_clusters <= 0) return fail(MUP_ERR_UNSUPPORTED, "no 2-CTA cluster fits on device %d", device);
-    int clusters = info.sms / 2;
-    if (clusters > max_clusters) clusters = max_clusters;
-    p.tile_n = choose_tile_n(p.m_tiles, n, clusters);
-    p.n_tiles = (n + p.tile_n - 1) / p.tile_n;
-    const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
-    p.split_tiles = choose_split_tiles(tiles, clusters, p.tile_n);
-    const long long items = tiles + p.split_tiles;
-    if (items < clusters) clusters = static_cast<int>(items);
-    core->grid = clusters * 2;
+    slots = std::min(info.sms / 2, max_clusters);
     core->smem_bytes = mup::GemmCfg<2>::kSmemBytes;
   }
+  Schedule schedule = choose_schedule(MODE, m_tiles, n, p.k_tiles, up, rank, g, slots);
+  const int clusters = static_cast<int>(std::min<size_t>(static_cast<size_t>(slots), schedule.items.size()));
+  core->grid = clusters * g;
   core->device = device;
   core->cta_group = g;
+  core->host_items = std::move(schedule.items);
+  core->model_cycles = schedule.critical_cycles;
+  p.num_items = static_cast<int>(core->host_items.size());
+  p.max_item_cols = schedule.max_cols;
+  p.row_len = p.row_base = p.row_extra = 0;
+  // The list lives in device memory for the life of the plan.
+  const size_t bytes = core->host_items.size() * sizeof(uint32_t);
+  void* table = nullptr;
+  MUP_CUDA(cudaMalloc(&table, bytes));
+  cudaError_t e = cudaMemcpy(table, core->host_items.data(), bytes, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    cudaFree(table);
+    return fail(MUP_ERR_CUDA, "uploading the work-item list failed: %s", cudaGetErrorString(e));
+  }
+  core->device_items = table;
+  p.items = static_cast<const uint32_t*>(table);
   if (const char* env = getenv("MEGA_UP_KERNEL_FLAGS")) p.flags = static_cast<unsigned int>(atoi(env));
+  return MUP_OK;
+}
+
+// W tensor maps: box j holds the rows one CTA loads for a part of (j + 1) * 64 columns.
+int encode_weight_maps(mup::GemmParams* p, const void* weight, int n, int k, int g) {
+  for (int j = 0; j < mup::kNumBMaps; ++j) {
+    const int rc = encode_map(&p->map_b[j], weight, k, n, k, mup::kBlockK, (j + 1) * mup::kUnit / g);
+    if (rc != MUP_OK) return rc;
+  }
+  return MUP_OK;
+}
+
+// Launches go to the device the plan was made for: the kernel's tensor maps,
+// its work-item list and (pull) its counters live there.
+int check_current_device(int device, const char* what) {
+  int current = -1;
+  MUP_CUDA(cudaGetDevice(&current));
+  if (current != device)
+    return fail(MUP_ERR_BAD_ARG, "%s was made for device %d but the current device is %d; call cudaSetDevice first",
+                what, device, current);
   return MUP_OK;
 }
 
@@ -541,6 +725,8 @@ __global__ void regroup_rows_kernel(uint4* __restrict__ dst, const uint4* __rest
 __global__ void gather_rows_synced_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
                                           const int64_t* __restrict__ index, int64_t rows,
                                           int64_t vecs, mup::SyncParams sp) {
+  mup::grid_dep_launch();
+  mup::grid_dep_wait();  // this rank's own earlier kernels (they wrote or still read what is copied here)
   // threads 0 .. up-1 poll one peer's flag each; the block proceeds on a unanimous vote
   const int handed = __syncthreads_and(mup::sync_wait_one(sp, static_cast<int>(threadIdx.x)) ? 1 : 0);
   if (handed) {
@@ -561,6 +747,8 @@ __global__ void gather_rows_synced_kernel(uint4* __restrict__ dst, const uint4* 
 __global__ void regroup_rows_synced_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
                                            int up, int batch, int64_t seq, int64_t vecs,
                                            int to_batch_major, mup::SyncParams sp) {
+  mup::grid_dep_launch();
+  mup::grid_dep_wait();  // this rank's own earlier kernels (they wrote or still read what is copied here)
   // threads 0 .. up-1 poll one peer's flag each; the block proceeds on a unanimous vote
   const int handed = __syncthreads_and(mup::sync_wait_one(sp, static_cast<int>(threadIdx.x)) ? 1 : 0);
   if (handed) {
@@ -593,9 +781,22 @@ __global__ void regroup_rows_synced_kernel(uint4* __restrict__ dst, const uint4*
 // Grid of a copy that carries a hand-off: at most the blocks that are resident
 // at once (8 x 256 threads per SM), so that every block's wait is paid once,
 // concurrently, and the arrival counter sees few atomics.
+int device_sm_count() {
+  // the copies run on the current device; cache its SM count per device ordinal
+  static int cached[64] = {0};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+  if (cached[device] == 0) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) return 148;
+    cached[device] = sms;
+  }
+  return cached[device];
+}
+
 int synced_copy_grid(int64_t total_vecs) {
   int64_t blocks = (total_vecs + 255) / 256;
-  const int64_t cap = 148 * 8;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return static_cast<int>(blocks);
@@ -603,7 +804,7 @@ int synced_copy_grid(int64_t total_vecs) {
 
 int copy_grid(int64_t total_vecs) {
   int64_t blocks = (total_vecs + 255) / 256;
-  const int64_t cap = 148 * 16;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return static_cast<int>(blocks);
@@ -635,6 +836,31 @@ int mup_shape_rule(int64_t width, int up) { return shape_rule(width, up); }
 int mup_peer_n_rotation(int rank, int up, int n_total, int tile_n) {
   if (up <= 0 || n_total <= 0 || tile_n <= 0 || rank < 0) return 0;
   return n_rotation(rank, up, n_total, tile_n);
+}
+
+// ---------------------------------------------------------------- schedule preview
+
+int mup_schedule_preview(int mode, int rows, int n, int k, int up, int rank, int cta_group, int slots,
+                         uint32_t* items, int capacity, int* count, int* max_item_cols,
+                         double* model_cycles) {
+  if (mode != mup::MODE_PEER_WRITE && mode != mup::MODE_PULL) return fail(MUP_ERR_BAD_ARG, "mode must be 0 or 1");
+  if (rows <= 0 || n <= 0 || k <= 0 || n % 256 || slots <= 0 || up < 1 || rank < 0 || rank >= up)
+    return fail(MUP_ERR_BAD_ARG, "bad schedule arguments");
+  if (cta_group < 0 || cta_group > 2) return fail(MUP_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
+  const int g = (cta_group == 0) ? 2 : cta_group;
+  const int m_tiles = (rows + mup::kBlockM * g - 1) / (mup::kBlockM * g);
+  if (m_tiles > mup::kMaxItemMTiles || n / mup::kUnit > mup::kMaxItemNUnits)
+    return fail(MUP_ERR_UNSUPPORTED, "rows=%d or n=%d exceeds the schedule's range", rows, n);
+  const Schedule schedule =
+      choose_schedule(mode, m_tiles, n, (k + mup::kBlockK - 1) / mup::kBlockK, up, rank, g, slots);
+  if (count != nullptr) *count = static_cast<int>(schedule.items.size());
+  if (max_item_cols != nullptr) *max_item_cols = schedule.max_cols;
+  if (model_cycles != nullptr) *model_cycles = schedule.critical_cycles;
+  if (items != nullptr) {
+    const size_t copy = std::min(schedule.items.size(), static_cast<size_t>(capacity < 0 ? 0 : capacity));
+    memcpy(items, schedule.items.data(), copy * sizeof(uint32_t));
+  }
+  return MUP_OK;
 }
 
 // ---------------------------------------------------------------- status
@@ -837,12 +1063,10 @@ int mup_peer_write_plan_create(mup_peer_write_plan** out, int device, int rows, 
   if (rc == MUP_OK) {
     const int g = plan->core.cta_group;
     p.shard = n / up;
-    p.n_rot = n_rotation(rank, up, n, p.tile_n);
     p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.status = static_cast<uint32_t*>(status_device_ptr);
     p.timeout_ns = timeout_ns;
-    rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, p.tile_n / g);
-    if (rc == MUP_OK) rc = encode_map(&p.map_b_half, weight, k, n, k, mup::kBlockK, p.tile_n / (2 * g));
+    rc = encode_weight_maps(&p, weight, n, k, g);
     for (int d = 0; d < up && rc == MUP_OK; ++d) {
       if (slot_ptrs[d] == nullptr) rc = fail(MUP_ERR_BAD_ARG, "slot pointer %d is null", d);
       if (rc == MUP_OK)
@@ -861,6 +1085,8 @@ int mup_peer_write_plan_create(mup_peer_write_plan** out, int device, int rows, 
 int mup_peer_write_launch(mup_peer_write_plan* plan, const void* a, void* stream) {
   if (plan == nullptr || a == nullptr) return fail(MUP_ERR_BAD_ARG, "null argument");
   mup::GemmParams& p = plan->core.params;
+  int rc_device = check_current_device(plan->core.device, "this peer-write plan");
+  if (rc_device != MUP_OK) return rc_device;
   if (a != plan->last_a) {
     int rc = encode_map(&p.map_a, a, p.K, p.M, p.K, mup::kBlockK, mup::kBlockM);
     if (rc != MUP_OK) return rc;
@@ -884,11 +1110,15 @@ int mup_peer_write_launch_synced(mup_peer_write_plan* plan, const void* a, void*
 
 int mup_peer_write_plan_info(const mup_peer_write_plan* plan, int* grid_ctas, int* cta_group,
                              int* n_rotation_out, int* smem_bytes, int* tile_n) {
-  if (plan != nullptr && tile_n != nullptr) *tile_n = plan->core.params.tile_n;
   if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
+  if (tile_n != nullptr) *tile_n = plan->core.params.max_item_cols;
   if (grid_ctas != nullptr) *grid_ctas = plan->core.grid;
   if (cta_group != nullptr) *cta_group = plan->core.cta_group;
-  if (n_rotation_out != nullptr) *n_rotation_out = plan->core.params.n_rot;
+  // first column of the first work item, in 256-column blocks
+  if (n_rotation_out != nullptr)
+    *n_rotation_out = plan->core.host_items.empty()
+                          ? 0
+                          : static_cast<int>((plan->core.host_items[0] >> 14) & 0xFFFu) * mup::kUnit / mup::kBlockN;
   if (smem_bytes != nullptr) *smem_bytes = plan->core.smem_bytes;
   return MUP_OK;
 }
@@ -949,7 +1179,6 @@ int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k
   if (rc == MUP_OK) {
     const int g = plan->core.cta_group;
     p.shard = k / up;
-    p.n_rot = 0;
     p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.status = static_cast<uint32_t*>(status_device_ptr);
     p.timeout_ns = timeout_ns;
@@ -965,8 +1194,7 @@ int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k
       p.peers[i] = static_cast<const __nv_bfloat16*>(peer_arena_ptrs[i]);
     }
     if (rc == MUP_OK) rc = encode_map(&p.map_a, dy, k, rows, k, mup::kBlockK, mup::kBlockM);
-    if (rc == MUP_OK) rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, p.tile_n / g);
-    if (rc == MUP_OK) rc = encode_map(&p.map_b_half, weight, k, n, k, mup::kBlockK, p.tile_n / (2 * g));
+    if (rc == MUP_OK) rc = encode_weight_maps(&p, weight, n, k, g);
     if (rc == MUP_OK)
       rc = encode_map(&p.map_out[0], out_buf, n, rows, n, mup::kEpiCols, mup::kEpiRows);
     plan->workspace = workspace;
@@ -985,6 +1213,8 @@ int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k
 int mup_pull_launch(mup_pull_plan* plan, void* stream) {
   if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
   mup::GemmParams& p = plan->core.params;
+  int rc_device = check_current_device(plan->core.device, "this pull plan");
+  if (rc_device != MUP_OK) return rc_device;
   // Tickets are drawn in chunks; every pull warp draws exactly one chunk past
   // the end before it stops, so a launch advances the cursor by chunks + pull_warps.
   const unsigned long long block = plan->pull_warps * mup::kPullChunk;
@@ -1021,8 +1251,8 @@ int mup_pull_plan_reset(mup_pull_plan* plan, void* stream) {
 
 int mup_pull_plan_info(const mup_pull_plan* plan, int* grid_ctas, int* cta_group,
                        uint64_t* launches, int* smem_bytes, int* tile_n) {
-  if (plan != nullptr && tile_n != nullptr) *tile_n = plan->core.params.tile_n;
   if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
+  if (tile_n != nullptr) *tile_n = plan->core.params.max_item_cols;
   if (grid_ctas != nullptr) *grid_ctas = plan->core.grid;
   if (cta_group != nullptr) *cta_group = plan->core.cta_group;
   if (launches != nullptr) *launches = plan->launches;
@@ -1137,6 +1367,9 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
   const NoAllocDevice* dev = nullptr;
   int rc = noalloc_setup(device, &dev);
   if (rc != MUP_OK) return rc;
+  // The scratch address belongs to `device`; the memset and the launch below go to the current device.
+  rc = check_current_device(device, "the allocation-free pull (argument `device`)");
+  if (rc != MUP_OK) return rc;
 
   const int g = (cta_group == 0) ? 2 : cta_group;
   mup::GemmParams p;  // on the stack: nothing here touches the heap or the device allocator
@@ -1147,18 +1380,39 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
   p.up = up;
   p.rank = rank;
   p.shard = k / up;
-  p.m_tiles = (rows + mup::kBlockM * g - 1) / (mup::kBlockM * g);
-  {
-    int slots = dev->sms;
-    if (g == 2) {
-      slots = dev->sms / 2;
-      if (slots > dev->max_clusters) slots = dev->max_clusters;
-      if (slots <= 0) return fail(MUP_ERR_UNSUPPORTED, "no 2-CTA cluster fits on device %d", device);
-    }
-    p.tile_n = choose_tile_n(p.m_tiles, n, slots);
+  const int m_tiles = (rows + mup::kBlockM * g - 1) / (mup::kBlockM * g);
+  p.k_tiles = (k + mup::kBlockK - 1) / mup::kBlockK;
+  int slots = dev->sms;
+  if (g == 2) {
+    slots = dev->sms / 2;
+    if (slots > dev->max_clusters) slots = dev->max_clusters;
+    if (slots <= 0) return fail(MUP_ERR_UNSUPPORTED, "no 2-CTA cluster fits on device %d", device);
   }
-  p.n_tiles = (n + p.tile_n - 1) / p.tile_n;
-  p.k_tiles = (k + mup::kStageK - 1) / mup::kStageK;
+  // No work-item list here (it would have to live in device memory): every M
+  // tile is cut into the same row_len items, the count that the time model
+  // rates best, and the kernel derives an item from its index.
+  {
+    const int units = n / mup::kUnit;
+    const int max_units = mup::max_item_cols(g) / mup::kUnit;
+    const int q_min = (units + max_units - 1) / max_units;
+    const double port_bpc = model_port_bytes_per_cycle();
+    int best_q = q_min;
+    double best_cost = -1.0;
+    for (int q = q_min; q <= units; ++q) {
+      const long long rounds = (static_cast<long long>(m_tiles) * q + slots - 1) / slots;
+      const double cost = rounds * item_cycles((units + q - 1) / q, p.k_tiles, g, port_bpc);
+      if (best_cost < 0.0 || cost < best_cost * 0.999) {
+        best_cost = cost;
+        best_q = q;
+      }
+    }
+    p.items = nullptr;
+    p.row_len = best_q;
+    p.row_base = units / best_q;
+    p.row_extra = units % best_q;
+    p.num_items = m_tiles * best_q;
+    p.max_item_cols = ((units + best_q - 1) / best_q) * mup::kUnit;
+  }
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.status = static_cast<uint32_t*>(status_device_ptr);
   p.timeout_ns = timeout_ns;
@@ -1175,22 +1429,11 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
     p.peers[i] = static_cast<const __nv_bfloat16*>(peer_arena_ptrs[i]);
   }
   rc = encode_map(&p.map_a, dy, k, rows, k, mup::kBlockK, mup::kBlockM);
-  if (rc == MUP_OK) rc = encode_map(&p.map_b, weight, k, n, k, mup::kBlockK, p.tile_n / g);
+  if (rc == MUP_OK) rc = encode_weight_maps(&p, weight, n, k, g);
   if (rc == MUP_OK) rc = encode_map(&p.map_out[0], out_buf, n, rows, n, mup::kEpiCols, mup::kEpiRows);
   if (rc != MUP_OK) return rc;
 
-  const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
-  int grid = 0;
-  if (g == 1) {
-    grid = static_cast<int>(tiles < dev->sms ? tiles : dev->sms);
-  } else {
-    if (dev->max_clusters <= 0)
-      return fail(MUP_ERR_UNSUPPORTED, "no 2-CTA cluster fits on device %d", device);
-    int clusters = dev->sms / 2;
-    if (clusters > dev->max_clusters) clusters = dev->max_clusters;
-    if (tiles < clusters) clusters = static_cast<int>(tiles);
-    grid = clusters * 2;
-  }
+  const int grid = (p.num_items < slots ? p.num_items : slots) * g;
 
   p.pull_stride = grid * mup::kPullWarps;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1227,9 +1470,8 @@ int mup_gather_rows_synced(void* dst, const void* src, const int64_t* index, int
   mup::SyncParams sp;
   int rc = fill_sync(&sp, sync, static_cast<unsigned long long>(grid));
   if (rc != MUP_OK) return rc;
-  gather_rows_synced_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<uint4*>(dst), static_cast<const uint4*>(src), index, rows, vecs, sp);
-  MUP_CUDA(cudaGetLastError());
+  MUP_CUDA(launch_small(gather_rows_synced_kernel, grid, 256, static_cast<cudaStream_t>(stream),
+                        static_cast<uint4*>(dst), static_cast<const uint4*>(src), index, rows, vecs, sp));
   return MUP_OK;
 }
 
@@ -1246,10 +1488,9 @@ int mup_regroup_rows_synced(void* dst, const void* src, int up, int batch, int64
   mup::SyncParams sp;
   int rc = fill_sync(&sp, sync, static_cast<unsigned long long>(grid));
   if (rc != MUP_OK) return rc;
-  regroup_rows_synced_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<uint4*>(dst), static_cast<const uint4*>(src), up, batch, seq, vecs,
-      to_batch_major, sp);
-  MUP_CUDA(cudaGetLastError());
+  MUP_CUDA(launch_small(regroup_rows_synced_kernel, grid, 256, static_cast<cudaStream_t>(stream),
+                        static_cast<uint4*>(dst), static_cast<const uint4*>(src), up, batch, seq, vecs,
+                        to_batch_major, sp));
   return MUP_OK;
 }
 

@@ -9,21 +9,32 @@
 //                    already consume finished 128-row panels (replaces
 //                    all_to_all + permute + linear).
 //
-// Tile: 128 (M) x 256 (N) x 64 (K) per CTA. G = 1 runs one CTA per tile
-// (tcgen05 cta_group::1); G = 2 pairs two CTAs of a cluster on a 256x256
-// tile (cta_group::2): each CTA loads its own 128 rows of A and its own 128
-// rows of W, so no load is ever multicast.
+// Work items. The output is cut into items of 128*G rows by 64..512 columns
+// (a multiple of 64), listed by the host in the order they are consumed; CTA
+// (pair) c runs items c, c + #clusters, ... . An item wider than 256 columns is
+// computed as two parts that share every A tile: each K step loads A once and
+// feeds it to two accumulators, so a 512-wide item moves 48 KiB per CTA and
+// 1024 tensor cycles where two 256-wide tiles move 64 KiB. On this GPU the
+// delivery of operands from L2 (about 12 TB/s over all SMs), not the tensor
+// pipe, bounds 256-wide tiles at full clock; wide items bring the demand under
+// that limit. A part is one accumulator of at most 256 FP32 columns in TMEM;
+// the two 256-column halves of TMEM form a ring of accumulator slots that the
+// parts of consecutive items take in turn, so the epilogue of one part overlaps
+// the K loop of the next.
+//
+// G = 1 runs one CTA per item (tcgen05 cta_group::1); G = 2 pairs two CTAs of a
+// cluster on 256 rows (cta_group::2): each CTA loads its own 128 rows of A and
+// its own half of every W box, so no load is ever multicast.
 //
 // The FP32 accumulator of an output element is a single TMEM cell that
 // receives the K products in ascending order, 16 at a time; bias is added in
-// FP32 and the sum is rounded to BF16 once. Nothing about the schedule (tile
-// width, which SM runs which tile, the half-width items of a partly filled
-// last wave) changes that order, so every configuration gives the same bits.
+// FP32 and the sum is rounded to BF16 once. Nothing about the schedule (item
+// widths, which SM runs which item, the order of items) changes that order, so
+// every schedule gives the same bits.
 //
-// Schedule: persistent CTAs, static round-robin over work items in N-fastest
-// order (peer-write: each rank starts at its own column block). The kernel
-// is launched with programmatic stream serialization: it lets its successor
-// be scheduled at entry and waits for its predecessor after its own set-up.
+// The kernel is launched with programmatic stream serialization: it lets its
+// successor be scheduled at entry and waits for its predecessor after its own
+// set-up.
 //
 // Warp roles (192 threads, 384 in pull mode):
 //   warp 0      TMA producer (one elected lane)
@@ -42,22 +53,19 @@
 namespace mup {
 
 constexpr int kBlockM = 128;
-constexpr int kBlockN = 256;
+constexpr int kBlockN = 256;          // columns of one accumulator slot (half of TMEM)
 constexpr int kBlockK = 64;           // K extent of one TMA box (128 bytes, the swizzle span)
-#ifndef MUP_KSUB
-#define MUP_KSUB 1
-#endif
-constexpr int kKSub = MUP_KSUB;              // boxes per pipeline stage (2 = 128-K stages with 8 MMAs per barrier round:
-                                      // measured no faster, 3 deep stages hide less latency than 6 shallow ones)
-constexpr int kStageK = kBlockK * kKSub;
 constexpr int kUmmaK = 16;
 constexpr int kMaxPeers = 8;
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = 512;
-constexpr int kEpiCols = 64;        // columns per epilogue sub-tile (128 bytes)
+constexpr int kEpiCols = 64;        // columns per epilogue sub-tile (128 bytes) = schedule granularity
 constexpr int kEpiRows = 32;        // rows per epilogue warp
 constexpr int kEpiBufBytes = kEpiRows * kEpiCols * 2;  // 4096
 constexpr int kEpiBufs = 2;
+constexpr int kUnit = kEpiCols;       // item widths and offsets are multiples of this
+constexpr int kMaxItemUnits = 8;      // 512 columns: both accumulator slots
+constexpr int kNumBMaps = 4;          // W boxes for parts of 64, 128, 192 and 256 columns
 #ifndef MUP_PULL_MAX_VECS
 #define MUP_PULL_MAX_VECS 512
 #endif
@@ -79,10 +87,9 @@ constexpr uint32_t ST_PULL_READY_TIMEOUT = 5;
 constexpr uint32_t ST_SMEM_MISALIGNED = 6;
 constexpr uint32_t ST_FLAG_TIMEOUT = 7;
 
-// Shared-memory plan. The N width of a tile (`tile_n`: 128, 192 or 256) and with
-// it the size and number of pipeline stages are chosen per problem on the
-// host, so the layout keeps a fixed 192 KiB stage area and room for the
-// largest stage count.
+// Shared-memory plan. The widest item of a launch fixes the size and with it
+// the number of pipeline stages, so the layout keeps a fixed 192 KiB stage
+// area and room for the largest stage count.
 constexpr int kMaxStages = 8;
 constexpr int kStageAreaBytes = 196608;
 template <int G>
@@ -99,21 +106,32 @@ struct GemmCfg {
   static constexpr int kUmmaM = kBlockM * G;
 };
 
-// W rows one CTA loads per stage, bytes of a stage, number of stages.
-__host__ __device__ constexpr int tile_b_rows(int tile_n, int g) { return tile_n / g; }
-__host__ __device__ constexpr int tile_stage_bytes(int tile_n, int g) {
-  return kKSub * (kBlockM * kBlockK * 2 + tile_b_rows(tile_n, g) * kBlockK * 2);
+// Widest item a CTA grouping can run: a lone CTA loads all W rows of an item
+// itself, so two parts would not leave room for enough stages.
+__host__ __device__ constexpr int max_item_cols(int g) { return g == 2 ? kMaxItemUnits * kUnit : kBlockN; }
+// W rows one CTA loads per K step for `cols` output columns, bytes of a stage, number of stages.
+__host__ __device__ constexpr int tile_b_rows(int cols, int g) { return cols / g; }
+__host__ __device__ constexpr int tile_stage_bytes(int cols, int g) {
+  return kBlockM * kBlockK * 2 + tile_b_rows(cols, g) * kBlockK * 2;
 }
-__host__ __device__ constexpr int tile_stages(int tile_n, int g) {
-  return kStageAreaBytes / tile_stage_bytes(tile_n, g) > kMaxStages
+__host__ __device__ constexpr int tile_stages(int cols, int g) {
+  return kStageAreaBytes / tile_stage_bytes(cols, g) > kMaxStages
              ? kMaxStages
-             : kStageAreaBytes / tile_stage_bytes(tile_n, g);
+             : kStageAreaBytes / tile_stage_bytes(cols, g);
 }
+
+// A work item as the host lists it: 14 bits M tile, 12 bits first column / 64, 3 bits (columns / 64 - 1).
+__host__ __device__ constexpr uint32_t encode_item(int m_idx, int n0_units, int w_units) {
+  return static_cast<uint32_t>(m_idx) | (static_cast<uint32_t>(n0_units) << 14) |
+         (static_cast<uint32_t>(w_units - 1) << 26);
+}
+constexpr uint32_t kNoItem = 0xFFFFFFFFu;  // a list entry without work (the CTA pair sits this round out)
+constexpr int kMaxItemMTiles = 1 << 14;
+constexpr int kMaxItemNUnits = 1 << 12;
 
 struct GemmParams {
   CUtensorMap map_a;                 // A  [M, K]   box 64 x 128
-  CUtensorMap map_b;                 // W  [N, K]   box 64 x (tile_n/G)
-  CUtensorMap map_b_half;            // W  [N, K]   box 64 x (tile_n/2G), for the split tail tiles
+  CUtensorMap map_b[kNumBMaps];      // W  [N, K]   box 64 x ((j + 1) * 64 / G): this CTA's rows of a part of (j + 1) * 64 columns
   CUtensorMap map_out[kMaxPeers];    // peer-write: [rows, shard] slot in peer p; pull: [0] = out [M, N]
   const __nv_bfloat16* bias;         // nullptr when absent
   uint32_t* status;                  // error word (host-visible)
@@ -121,10 +139,14 @@ struct GemmParams {
   int M, N, K;
   int shard;                         // exchanged columns per rank
   int up, rank;
-  int n_rot;                         // peer-write: first N tile of this rank
-  int m_tiles, n_tiles, k_tiles;     // m_tiles counts (128*G)-row tiles, n_tiles tile_n-column tiles
-  int tile_n;                        // 128, 192 or 256 output columns per tile
-  int split_tiles;                   // this many trailing tiles are each run as two half-width tiles (0: none)
+  int k_tiles;
+  // Schedule: `items` lists the work items in consumption order. Without a list
+  // (nullptr) every M tile is cut alike: row_len items, the first row_extra of
+  // them row_base + 1 units wide and the rest row_base units.
+  const uint32_t* items;
+  int num_items;
+  int row_len, row_base, row_extra;
+  int max_item_cols;                 // widest item: fixes the stage size
   // pull mode only
   const __nv_bfloat16* peers[kMaxPeers];  // staged arenas [up(dest), peer_rows, shard]
   __nv_bfloat16* dy;                 // dense pulled input [M, K]
@@ -156,12 +178,17 @@ constexpr int kTracePullEndNs = 8;    // %globaltimer when this CTA's pull worke
 constexpr int kTracePullTickets = 9;  // tickets copied by this CTA's pull workers
 constexpr int kTraceGateFirstNs = 10; // ns from kernel entry until the producer's first panel gate opened
 constexpr int kTraceGateCycles = 11;  // producer cycles spent at panel gates
+constexpr int kTraceSetupNs = 12;     // ns from kernel entry until the predecessor kernel had completed (set-up done)
+constexpr int kTracePullFirstNs = 13; // ns from kernel entry until the first pull warp had stored its first ticket
+constexpr int kTraceFirstMmaNs = 14;  // ns from kernel entry until the first operands had landed (first MMA)
+constexpr int kTraceItems = 15;       // work items this CTA (pair) ran
 constexpr int kTraceSlots = 16;
 
 constexpr unsigned int kFlagNoL2Hints = 8u;     // tuning: drop the L2 hints (W loads evict-last, output stores evict-first)
 constexpr unsigned int kFlagSplitCommit = 1u;  // G=2: one commit per CTA of the pair instead of one for both
 constexpr unsigned int kFlagSeparateIssue = 2u;  // tuning: poll, MMAs and commit as separate statements (the slower issue loop)
 constexpr unsigned int kFlagPullExtraFence = 16u;  // tuning: an explicit fence.acq_rel.gpu before every release of a ready count
+constexpr unsigned int kFlagNoWPrefetch = 32u;  // tuning: pull mode, do not load W ahead of a closed panel gate
 
 __device__ __forceinline__ void report_status(const GemmParams& p, volatile uint32_t* abort_flag,
                                               uint32_t code, uint32_t detail) {
@@ -251,6 +278,48 @@ __host__ __device__ constexpr int kernel_threads(int mode) {
   return mode == MODE_PULL ? 192 + 32 * kPullWarps : 192;
 }
 
+// A decoded work item: `parts` accumulators of part_cols[] columns each, side by side from column n0.
+struct WorkItem {
+  int m_idx;
+  int n0;
+  int parts;
+  int part_cols[2];
+};
+
+__device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int item) {
+  int m_idx, n0_units, w_units;
+  if (p.items != nullptr) {
+    const uint32_t e = __ldg(p.items + item);
+    if (e == kNoItem) {
+      WorkItem none;
+      none.m_idx = none.n0 = none.parts = 0;
+      none.part_cols[0] = none.part_cols[1] = 0;
+      return none;
+    }
+    m_idx = static_cast<int>(e & 0x3FFFu);
+    n0_units = static_cast<int>((e >> 14) & 0xFFFu);
+    w_units = static_cast<int>((e >> 26) & 0x7u) + 1;
+  } else {
+    m_idx = item / p.row_len;
+    const int pos = item - m_idx * p.row_len;
+    n0_units = pos * p.row_base + (pos < p.row_extra ? pos : p.row_extra);
+    w_units = p.row_base + (pos < p.row_extra ? 1 : 0);
+  }
+  WorkItem w;
+  w.m_idx = m_idx;
+  w.n0 = n0_units * kUnit;
+  if (w_units * kUnit <= kBlockN) {
+    w.parts = 1;
+    w.part_cols[0] = w_units * kUnit;
+    w.part_cols[1] = 0;
+  } else {
+    w.parts = 2;
+    w.part_cols[0] = ((w_units + 1) >> 1) * kUnit;
+    w.part_cols[1] = (w_units >> 1) * kUnit;
+  }
+  return w;
+}
+
 template <int G, int MODE>
 __global__ void __launch_bounds__(kernel_threads(MODE), 1)
 fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
@@ -262,31 +331,9 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t cta_rank = (G == 2) ? cluster_ctarank() : 0u;
   const int cluster_id = blockIdx.x / G;
   const int num_clusters = gridDim.x / G;
-  const int num_tiles = p.m_tiles * p.n_tiles;
-  const int tile_n = p.tile_n;
-  const int num_stages = tile_stages(tile_n, G);
-  const uint32_t stage_bytes = static_cast<uint32_t>(tile_stage_bytes(tile_n, G));
-  // Work items: the tiles of the full waves, then the tiles of the last,
-  // partly filled wave cut into two half-width items each, so that the tail
-  // keeps about twice as many SMs busy for half as long. An item keeps the
-  // whole K loop of its columns, so the accumulation order is unchanged.
-  const int split_from = num_tiles - p.split_tiles;
-  const int num_items = num_tiles + p.split_tiles;
-  auto decode_item = [&](int item, int& m_idx, int& n0, int& width) {
-    int t = item;
-    int half = 0;
-    width = tile_n;
-    if (item >= split_from) {
-      const int j = item - split_from;
-      t = split_from + (j >> 1);
-      half = j & 1;
-      width = tile_n >> 1;
-    }
-    m_idx = t / p.n_tiles;
-    int n_blk = t - m_idx * p.n_tiles + p.n_rot;
-    if (n_blk >= p.n_tiles) n_blk -= p.n_tiles;
-    n0 = n_blk * tile_n + half * width;
-  };
+  const int num_items = p.num_items;
+  const int num_stages = tile_stages(p.max_item_cols, G);
+  const uint32_t stage_bytes = static_cast<uint32_t>(tile_stage_bytes(p.max_item_cols, G));
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_base = smem_base + Cfg::kOffBar;
@@ -318,7 +365,8 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
     fence_mbar_init();
     tma_prefetch_desc(&p.map_a);
-    tma_prefetch_desc(&p.map_b);
+#pragma unroll
+    for (int j = 0; j < kNumBMaps; ++j) tma_prefetch_desc(&p.map_b[j]);
   }
   if (warp == 1) {
     tmem_alloc<G>(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
@@ -335,29 +383,75 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const bool misaligned = (*abort_flag != 0u);
-  // Everything above touched only this CTA's shared memory and TMEM; from here
-  // on the kernel reads what earlier kernels of the stream wrote.
+  // Everything above touched only this CTA's shared memory and TMEM (and the
+  // launch parameters); from here on the kernel reads what earlier kernels of
+  // the stream wrote.
   grid_dep_wait();
+  if (trace != nullptr && threadIdx.x == 0) trace[kTraceSetupNs] = globaltimer_ns() - trace[kTraceNsStart];
 
   // ------------------------------------------------------------ TMA producer
   if (warp == 0 && !misaligned) {
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
-      uint32_t in_flight = 0;  // loads armed so far (saturates at kStages)
+      uint32_t in_flight = 0;  // loads armed so far (saturates at the stage count)
       bool ok = true;
       long long waited = 0;
       const uint32_t leader_full0 = (G == 2) ? mapa_cluster(full_bar(0), 0) : full_bar(0);
       const bool hints = (p.flags & kFlagNoL2Hints) == 0u;
-      const uint64_t keep = l2_policy_evict_last();  // W is re-read by every wave of tiles
-      for (int tile = cluster_id; tile < num_items && ok; tile += num_clusters) {
-        int m_idx, n0, width;
-        decode_item(tile, m_idx, n0, width);
-        const int panel = m_idx * G + static_cast<int>(cta_rank);
+      const uint64_t keep = l2_policy_evict_last();  // W is re-read by every round of items
+      auto advance = [&](uint32_t& s, uint32_t& ph) {
+        if (++s == static_cast<uint32_t>(num_stages)) {
+          s = 0;
+          ph ^= 1u;
+        }
+      };
+      for (int item = cluster_id; item < num_items && ok; item += num_clusters) {
+        const WorkItem w = decode_item(p, item);
+        if (w.parts == 0) continue;
+        const int panel = w.m_idx * G + static_cast<int>(cta_rank);
         const int a_row0 = panel * kBlockM;
-        const int b_rows = tile_b_rows(width, G);
-        const int b_row0 = n0 + static_cast<int>(cta_rank) * b_rows;
-        const CUtensorMap* map_b = (width == tile_n) ? &p.map_b : &p.map_b_half;
-        const uint32_t item_bytes = static_cast<uint32_t>(tile_stage_bytes(width, G));
+        const int item_cols = w.part_cols[0] + w.part_cols[1];
+        const uint32_t item_bytes = static_cast<uint32_t>(tile_stage_bytes(item_cols, G));
+        // Arm a stage for the bytes of one K step of this item (for a CTA pair
+        // both CTAs' loads complete on the leader's barrier, armed for both).
+        auto arm = [&](uint32_t s) {
+          if constexpr (G == 1) {
+            mbar_arrive_expect_tx(full_bar(s), item_bytes);
+          } else {
+            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * item_bytes);
+          }
+        };
+        auto load_a = [&](uint32_t s, int kt) {
+          const uint32_t dst = smem_base + s * stage_bytes;
+          const uint32_t bar = (G == 2) ? leader_full0 + 8u * s : full_bar(s);
+          if constexpr (G == 1) {
+            if (hints) tma_load_2d_hint(dst, &p.map_a, kt * kBlockK, a_row0, bar, keep);
+            else tma_load_2d(dst, &p.map_a, kt * kBlockK, a_row0, bar);
+          } else {
+            if (hints) tma_load_2d_pair_hint(dst, &p.map_a, kt * kBlockK, a_row0, bar, keep);
+            else tma_load_2d_pair(dst, &p.map_a, kt * kBlockK, a_row0, bar);
+          }
+        };
+        auto load_w = [&](uint32_t s, int kt) {
+          uint32_t dst = smem_base + s * stage_bytes + Cfg::kABytes;
+          const uint32_t bar = (G == 2) ? leader_full0 + 8u * s : full_bar(s);
+          int col0 = w.n0;
+          for (int part = 0; part < w.parts; ++part) {
+            const int rows = tile_b_rows(w.part_cols[part], G);
+            const CUtensorMap* map = &p.map_b[w.part_cols[part] / kUnit - 1];
+            const int row0 = col0 + static_cast<int>(cta_rank) * rows;
+            if constexpr (G == 1) {
+              if (hints) tma_load_2d_hint(dst, map, kt * kBlockK, row0, bar, keep);
+              else tma_load_2d(dst, map, kt * kBlockK, row0, bar);
+            } else {
+              if (hints) tma_load_2d_pair_hint(dst, map, kt * kBlockK, row0, bar, keep);
+              else tma_load_2d_pair(dst, map, kt * kBlockK, row0, bar);
+            }
+            dst += static_cast<uint32_t>(rows) * kBlockK * 2;
+            col0 += w.part_cols[part];
+          }
+        };
+        int kt_begin = 0;
         if constexpr (MODE == MODE_PULL) {
           // Gate on the pull workers having finished this 128-row panel.
           const int groups_per_panel = kBlockM / p.pull_rows;
@@ -366,11 +460,25 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           groups = groups < 0 ? 0 : (groups > groups_per_panel ? groups_per_panel : groups);
           const unsigned long long want = p.epoch1 * static_cast<unsigned long long>(groups) *
                                           static_cast<unsigned long long>(p.up) * static_cast<unsigned long long>(p.pull_segs);
-          if (groups > 0) {
+          const uint64_t* ready = reinterpret_cast<const uint64_t*>(p.ready + panel);
+          if (groups > 0 && ld_acquire_gpu_u64(ready) < want) {
+            // The panel is still being pulled. W does not depend on it: arm the
+            // stages that are free right now and load their W boxes, so that only
+            // the A boxes remain to be fetched once the gate opens.
+            int pre = 0;
+            if ((p.flags & kFlagNoWPrefetch) == 0u) {
+              uint32_t s = stage, ph = phase;
+              while (pre < num_stages && pre < p.k_tiles && mbar_test_wait(empty_bar(s), ph ^ 1u)) {
+                arm(s);
+                load_w(s, pre);
+                advance(s, ph);
+                ++pre;
+              }
+            }
             const uint64_t t0 = globaltimer_ns();
             const long long gate_c0 = trace ? clock64() : 0;
             uint32_t it = 0;
-            while (ld_acquire_gpu_u64(reinterpret_cast<const uint64_t*>(p.ready + panel)) < want) {
+            while (ld_acquire_gpu_u64(ready) < want) {
               if ((++it & 0x3fu) == 0) {
                 if (*abort_flag != 0u || globaltimer_ns() - t0 > timeout_ns) {
                   report_status(p, abort_flag, ST_PULL_READY_TIMEOUT, static_cast<uint32_t>(panel));
@@ -380,66 +488,46 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
                 __nanosleep(64);
               }
             }
-            if (!ok) break;
-            if (trace) {
-              trace[kTraceGateCycles] += static_cast<unsigned long long>(clock64() - gate_c0);
-              if (trace[kTraceGateFirstNs] == 0) trace[kTraceGateFirstNs] = globaltimer_ns() - trace[kTraceNsStart];
+            if (trace) trace[kTraceGateCycles] += static_cast<unsigned long long>(clock64() - gate_c0);
+            if (ok) fence_proxy_async_all();  // generic-proxy writes of dy -> async-proxy (TMA) reads
+            // Armed stages get their A boxes even when giving up (with the gate
+            // closed the rows are stale, never out of bounds), so that every armed
+            // barrier completes and the drain below can count on it.
+            for (int j = 0; j < pre; ++j) {
+              load_a(stage, j);
+              if (in_flight < static_cast<uint32_t>(num_stages)) ++in_flight;
+              advance(stage, phase);
             }
-            fence_proxy_async_all();  // generic-proxy writes of dy -> async-proxy (TMA) reads
+            kt_begin = pre;
+            if (!ok) break;
+          } else if (groups > 0) {
+            fence_proxy_async_all();
           }
+          if (trace && trace[kTraceGateFirstNs] == 0) trace[kTraceGateFirstNs] = globaltimer_ns() - trace[kTraceNsStart];
         }
-        for (int kt = 0; kt < p.k_tiles; ++kt) {
+        for (int kt = kt_begin; kt < p.k_tiles; ++kt) {
           const long long t_wait = trace ? clock64() : 0;
           const bool free_stage = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, timeout_ns);
           if (trace) waited += clock64() - t_wait;
           if (!free_stage) {
-            report_status(p, abort_flag, ST_PRODUCER_SLOT_TIMEOUT, static_cast<uint32_t>(tile));
+            report_status(p, abort_flag, ST_PRODUCER_SLOT_TIMEOUT, static_cast<uint32_t>(item));
             ok = false;
             break;
           }
-          // Stage layout: [A box 0][A box 1][B box 0][B box 1], every box 64 K elements wide.
-          const uint32_t a_dst = smem_base + stage * stage_bytes;
-          const uint32_t b_dst = a_dst + kKSub * Cfg::kABytes;
-          const uint32_t b_box_bytes = static_cast<uint32_t>(b_rows) * kBlockK * 2;
-          if constexpr (G == 1) {
-            mbar_arrive_expect_tx(full_bar(stage), item_bytes);
-#pragma unroll
-            for (int sub = 0; sub < kKSub; ++sub) {
-              const int kcol = kt * kStageK + sub * kBlockK;
-              tma_load_2d(a_dst + sub * Cfg::kABytes, &p.map_a, kcol, a_row0, full_bar(stage));
-              if (hints) {
-                tma_load_2d_hint(b_dst + sub * b_box_bytes, map_b, kcol, b_row0, full_bar(stage), keep);
-              } else {
-                tma_load_2d(b_dst + sub * b_box_bytes, map_b, kcol, b_row0, full_bar(stage));
-              }
-            }
-          } else {
-            // Both CTAs' loads complete on the leader's barrier, which the
-            // leader arms for the bytes of the whole pair.
-            const uint32_t bar = leader_full0 + 8u * stage;
-            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * item_bytes);
-#pragma unroll
-            for (int sub = 0; sub < kKSub; ++sub) {
-              const int kcol = kt * kStageK + sub * kBlockK;
-              tma_load_2d_pair(a_dst + sub * Cfg::kABytes, &p.map_a, kcol, a_row0, bar);
-              if (hints) {
-                tma_load_2d_pair_hint(b_dst + sub * b_box_bytes, map_b, kcol, b_row0, bar, keep);
-              } else {
-                tma_load_2d_pair(b_dst + sub * b_box_bytes, map_b, kcol, b_row0, bar);
-              }
-            }
-          }
+          // Stage layout: [A box][W box of part 0][W box of part 1], every box 64 K elements wide.
+          arm(stage);
+          load_a(stage, kt);
+          load_w(stage, kt);
           if (in_flight < static_cast<uint32_t>(num_stages)) ++in_flight;
-          if (++stage == static_cast<uint32_t>(num_stages)) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          advance(stage, phase);
         }
       }
       if (trace) trace[kTraceProdWait] = static_cast<unsigned long long>(waited);
-      if (!ok && G == 1) {
+      if (!ok) {
         // Giving up: let loads that are still in flight land before the CTA
-        // retires (their barrier completes without any consumer).
+        // retires. A lone CTA (and the leader of a pair) watches its own full
+        // barriers; the other CTA of a pair has no barrier of its own to watch
+        // and allows the same 2 ms per stage.
         uint32_t s = stage, ph = phase;
         for (uint32_t i = 0; i < in_flight; ++i) {
           if (s == 0) {
@@ -448,7 +536,12 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
           --s;
           const uint64_t t0 = globaltimer_ns();
-          while (!mbar_try_wait(full_bar(s), ph) && globaltimer_ns() - t0 < 2000000ull) {
+          if (G == 1 || cta_rank == 0) {
+            while (!mbar_try_wait(full_bar(s), ph) && globaltimer_ns() - t0 < 2000000ull) {
+            }
+          } else {
+            while (globaltimer_ns() - t0 < 2000000ull / static_cast<uint64_t>(num_stages)) {
+            }
           }
         }
       }
@@ -461,109 +554,123 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   // per 64-wide K step, 512 of them tensor-pipe work at N = 256): ~770 for a loop
   // run by a single lane inside a divergent branch, ~560 for the warp-uniform
   // loop with poll, four MMAs and commit as separate statements, 512 for the
-  // fused sequence used here (umma_kstep4_probe_next), which also keeps the pipe
-  // full at N = 128. In the full kernel the last step makes no measurable
-  // difference: the K loop is then limited by operand delivery from L2.
+  // fused sequence used here (umma_kstep4_probe_next / umma_kstep8_probe_next),
+  // which also keeps the pipe full at N = 128. The first and the last K step of
+  // an item use separate statements: the first waits for each accumulator slot
+  // just before the MMAs that overwrite it, the last publishes each part's
+  // accumulator as soon as that part's MMAs are issued.
   if (warp == 1 && !misaligned && cta_rank == 0) {
-    const uint32_t idesc_full = make_idesc_bf16(Cfg::kUmmaM, tile_n);
-    const uint32_t idesc_half = make_idesc_bf16(Cfg::kUmmaM, tile_n >> 1);
     const uint64_t desc0 = make_kmajor_sw128_desc(smem_base);
     const uint64_t desc_step = static_cast<uint64_t>(stage_bytes >> 4);
     const bool pair_commit = (G == 2) && (p.flags & kFlagSplitCommit) == 0u;
-    // The fused step needs one TMA box per stage and, for a CTA pair, the commit
-    // that reaches both CTAs' barriers at once.
-    const bool fused_step = (kKSub == 1) && (G == 1 || pair_commit) && (p.flags & kFlagSeparateIssue) == 0u;
+    // The fused step needs, for a CTA pair, the commit that reaches both CTAs' barriers at once.
+    const bool fused_ok = (G == 1 || pair_commit) && (p.flags & kFlagSeparateIssue) == 0u;
+    auto commit_to = [&](uint32_t bar) {
+      if constexpr (G == 1) {
+        umma_commit_1(bar);
+      } else {
+        if (pair_commit) {
+          umma_commit_2_mask(bar, 3);
+        } else {
+          umma_commit_2(mapa_cluster(bar, 0));
+          umma_commit_2(mapa_cluster(bar, 1));
+        }
+      }
+    };
     uint32_t stage = 0, phase = 0;
-    uint32_t acc_it = 0;
+    uint32_t acc_it = 0;  // parts issued so far: part i uses accumulator slot i & 1
     bool failed = false;
     bool stage_ready = false;  // the probe of the previous step found this stage full
+    bool first_mma = true;
     long long wait_full = 0, wait_acc = 0;
-    for (int tile = cluster_id; tile < num_items; tile += num_clusters, ++acc_it) {
-      const uint32_t as = acc_it & 1u;
-      const uint32_t aphase = (acc_it >> 1) & 1u;
-      const bool half_item = tile >= split_from;
-      const uint32_t idesc = half_item ? idesc_half : idesc_full;
-      const uint64_t b_box_step =
-          static_cast<uint64_t>((tile_b_rows(half_item ? (tile_n >> 1) : tile_n, G) * kBlockK * 2) >> 4);
-      const long long t_acc = trace ? clock64() : 0;
-      if (!mbar_wait_bounded(acc_empty_bar(as), aphase ^ 1u, abort_flag, timeout_ns)) {
-        report_status(p, abort_flag, ST_MMA_ACC_TIMEOUT, static_cast<uint32_t>(tile));
-        failed = true;
+    int items_run = 0;
+    for (int item = cluster_id; item < num_items; item += num_clusters, ++items_run) {
+      const WorkItem w = decode_item(p, item);
+      if (w.parts == 0) continue;
+      uint32_t slot[2], d_tmem[2], idesc[2];
+      uint64_t b_off[2];
+      uint32_t b_bytes = 0;
+      for (int part = 0; part < 2; ++part) {
+        slot[part] = (acc_it + part) & 1u;
+        d_tmem[part] = tmem_base + slot[part] * kBlockN;
+        idesc[part] = make_idesc_bf16(Cfg::kUmmaM, w.part_cols[part] > 0 ? w.part_cols[part] : kUnit);
+        b_off[part] = static_cast<uint64_t>((Cfg::kABytes + b_bytes) >> 4);
+        b_bytes += static_cast<uint32_t>(tile_b_rows(w.part_cols[part], G)) * kBlockK * 2;
       }
-      if (trace) wait_acc += clock64() - t_acc;
-      tc_fence_after_sync();
-      const uint32_t d_tmem = tmem_base + as * kBlockN;
       for (int kt = 0; kt < p.k_tiles; ++kt) {
         if (!stage_ready) {
           const long long t_full = trace ? clock64() : 0;
           if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, timeout_ns)) {
-            report_status(p, abort_flag, ST_MMA_FULL_TIMEOUT, static_cast<uint32_t>(tile));
+            report_status(p, abort_flag, ST_MMA_FULL_TIMEOUT, static_cast<uint32_t>(item));
             failed = true;
           }
           if (trace) wait_full += clock64() - t_full;
           tc_fence_after_sync();
         }
+        if (trace && first_mma && lane == 0) trace[kTraceFirstMmaNs] = globaltimer_ns() - trace[kTraceNsStart];
+        first_mma = false;
         const uint64_t a_desc = desc0 + desc_step * stage;
-        const uint64_t b_desc = a_desc + static_cast<uint64_t>((kKSub * Cfg::kABytes) >> 4);
         uint32_t next_stage = stage + 1u, next_phase = phase;
         if (next_stage == static_cast<uint32_t>(num_stages)) {
           next_stage = 0;
           next_phase ^= 1u;
         }
-        if (fused_step) {
-          // Four MMAs, the commit that frees the stage and a probe of the next
-          // stage's barrier as one instruction sequence of the elected lane.
+        const bool edge = (kt == 0) || (kt == p.k_tiles - 1);
+        if (fused_ok && !edge) {
+          // The MMAs of the stage, the commit that frees it and a probe of the
+          // next stage's barrier as one instruction sequence of the elected lane.
           uint32_t probed = 0;
           if (elect_one_sync()) {
-            probed = umma_kstep4_probe_next<G>(d_tmem, a_desc, b_desc, idesc, kt > 0 ? 1u : 0u, empty_bar(stage),
-                                               full_bar(next_stage), next_phase);
+            if (w.parts == 1) {
+              probed = umma_kstep4_probe_next<G>(d_tmem[0], a_desc, a_desc + b_off[0], idesc[0], 1u,
+                                                 empty_bar(stage), full_bar(next_stage), next_phase);
+            } else {
+              probed = umma_kstep8_probe_next<G>(d_tmem[0], d_tmem[1], a_desc, a_desc + b_off[0], a_desc + b_off[1],
+                                                 idesc[0], idesc[1], empty_bar(stage), full_bar(next_stage),
+                                                 next_phase);
+            }
           }
           stage_ready = __any_sync(0xffffffffu, probed != 0u);
         } else {
-          if (elect_one_sync()) {
-            // Per box: 16 BF16 = 32 bytes further along K inside the 128-byte swizzle row per MMA.
-#pragma unroll
-            for (int sub = 0; sub < kKSub; ++sub) {
-              const uint64_t a_sub = a_desc + static_cast<uint64_t>(sub) * (Cfg::kABytes >> 4);
-              const uint64_t b_sub = b_desc + static_cast<uint64_t>(sub) * b_box_step;
-              umma_bf16<G>(d_tmem, a_sub, b_sub, idesc, (kt > 0 || sub > 0) ? 1u : 0u);
-              umma_bf16<G>(d_tmem, a_sub + 2, b_sub + 2, idesc, 1u);
-              umma_bf16<G>(d_tmem, a_sub + 4, b_sub + 4, idesc, 1u);
-              umma_bf16<G>(d_tmem, a_sub + 6, b_sub + 6, idesc, 1u);
+          for (int part = 0; part < w.parts; ++part) {
+            if (kt == 0) {
+              // This part overwrites its accumulator slot: the epilogue must have read the slot's previous part.
+              const uint32_t aphase = ((acc_it + part) >> 1) & 1u;
+              const long long t_acc = trace ? clock64() : 0;
+              if (!mbar_wait_bounded(acc_empty_bar(slot[part]), aphase ^ 1u, abort_flag, timeout_ns)) {
+                report_status(p, abort_flag, ST_MMA_ACC_TIMEOUT, static_cast<uint32_t>(item));
+                failed = true;
+              }
+              if (trace) wait_acc += clock64() - t_acc;
+              tc_fence_after_sync();
             }
-            // Release the shared-memory slot once these MMAs have read it.
-            if constexpr (G == 1) {
-              umma_commit_1(empty_bar(stage));
-            } else if (pair_commit) {
-              umma_commit_2_mask(empty_bar(stage), 3);
-            } else {
-              umma_commit_2(mapa_cluster(empty_bar(stage), 0));
-              umma_commit_2(mapa_cluster(empty_bar(stage), 1));
+            if (elect_one_sync()) {
+              // 16 BF16 = 32 bytes further along K inside the 128-byte swizzle row per MMA.
+              const uint64_t b_desc = a_desc + b_off[part];
+              umma_bf16<G>(d_tmem[part], a_desc, b_desc, idesc[part], kt > 0 ? 1u : 0u);
+              umma_bf16<G>(d_tmem[part], a_desc + 2, b_desc + 2, idesc[part], 1u);
+              umma_bf16<G>(d_tmem[part], a_desc + 4, b_desc + 4, idesc[part], 1u);
+              umma_bf16<G>(d_tmem[part], a_desc + 6, b_desc + 6, idesc[part], 1u);
+              // Publish the finished accumulator to the epilogue warps.
+              if (kt == p.k_tiles - 1) commit_to(acc_full_bar(slot[part]));
             }
           }
+          // Release the shared-memory stage once these MMAs have read it.
+          if (elect_one_sync()) commit_to(empty_bar(stage));
           stage_ready = false;
         }
         stage = next_stage;
         phase = next_phase;
       }
-      // Publish the finished accumulator to the epilogue warps.
-      if (elect_one_sync()) {
-        if constexpr (G == 1) {
-          umma_commit_1(acc_full_bar(as));
-        } else if (pair_commit) {
-          umma_commit_2_mask(acc_full_bar(as), 3);
-        } else {
-          umma_commit_2(mapa_cluster(acc_full_bar(as), 0));
-          umma_commit_2(mapa_cluster(acc_full_bar(as), 1));
-        }
-      }
+      acc_it += static_cast<uint32_t>(w.parts);
       // A lane whose wait ran out has raised the abort flag, which makes every
-      // later wait return at once; the warp leaves together at a tile boundary.
+      // later wait return at once; the warp leaves together at an item boundary.
       if (__any_sync(0xffffffffu, failed)) break;
     }
     if (trace && lane == 0) {
       trace[kTraceMmaWaitFull] = static_cast<unsigned long long>(wait_full);
       trace[kTraceMmaWaitAcc] = static_cast<unsigned long long>(wait_acc);
+      trace[kTraceItems] = static_cast<unsigned long long>(items_run);
     }
   }
 
@@ -579,124 +686,128 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     bool ok = true;
     long long epi_wait = 0;
     bool handoff_checked = false;
-    for (int tile = cluster_id; tile < num_items && ok; tile += num_clusters, ++acc_it) {
-      int m_idx, n0, width;
-      decode_item(tile, m_idx, n0, width);
-      const uint32_t as = acc_it & 1u;
-      const uint32_t aphase = (acc_it >> 1) & 1u;
-      const int row0 = (m_idx * G + static_cast<int>(cta_rank)) * kBlockM + q * kEpiRows;
+    for (int item = cluster_id; item < num_items && ok; item += num_clusters) {
+      const WorkItem w = decode_item(p, item);
+      if (w.parts == 0) continue;
+      const int row0 = (w.m_idx * G + static_cast<int>(cta_rank)) * kBlockM + q * kEpiRows;
+      int part_col0 = w.n0;
+      for (int part = 0; part < w.parts && ok; ++part, ++acc_it) {
+        const uint32_t as = acc_it & 1u;
+        const uint32_t aphase = (acc_it >> 1) & 1u;
 
-      const long long t_epi = trace ? clock64() : 0;
-      const bool got = mbar_wait_bounded(acc_full_bar(as), aphase, abort_flag, timeout_ns);
-      if (trace) epi_wait += clock64() - t_epi;
-      if (!__all_sync(0xffffffffu, got)) {
-        if (lane == 0) report_status(p, abort_flag, ST_EPILOGUE_TIMEOUT, static_cast<uint32_t>(tile));
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-
-      const int chunks = width / kEpiCols;
-      for (int c = 0; c < chunks; ++c) {
-        const int gcol = n0 + c * kEpiCols;
-        const bool in_range = gcol < p.N;  // the last tile of a row may hang over N
-        // Bias for these 64 columns, widened to FP32, shared inside the warp.
-        if (p.bias != nullptr && in_range) {
-          const __nv_bfloat162 b2 =
-              *reinterpret_cast<const __nv_bfloat162*>(p.bias + gcol + 2 * lane);
-          bias_s[2 * lane] = __bfloat162float(b2.x);
-          bias_s[2 * lane + 1] = __bfloat162float(b2.y);
+        const long long t_epi = trace ? clock64() : 0;
+        const bool got = mbar_wait_bounded(acc_full_bar(as), aphase, abort_flag, timeout_ns);
+        if (trace) epi_wait += clock64() - t_epi;
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) report_status(p, abort_flag, ST_EPILOGUE_TIMEOUT, static_cast<uint32_t>(item));
+          ok = false;
+          break;
         }
-        uint32_t v[2][32];
-        const uint32_t taddr =
-            tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kBlockN + c * kEpiCols;
-        tmem_ld_32x32(taddr, v[0]);
-        tmem_ld_32x32(taddr + 32, v[1]);
-        tmem_ld_wait();
-        if (c == chunks - 1) {
-          // Accumulator fully read: hand the TMEM stage back to the MMA warp.
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) {
-            if constexpr (G == 1) {
-              mbar_arrive(acc_empty_bar(as));
-            } else {
-              mbar_arrive_cluster(acc_empty_leader0 + 8u * as);
-            }
+        tc_fence_after_sync();
+
+        const int chunks = w.part_cols[part] / kEpiCols;
+        for (int c = 0; c < chunks; ++c) {
+          const int gcol = part_col0 + c * kEpiCols;
+          const bool in_range = gcol < p.N;
+          // Bias for these 64 columns, widened to FP32, shared inside the warp.
+          if (p.bias != nullptr && in_range) {
+            const __nv_bfloat162 b2 =
+                *reinterpret_cast<const __nv_bfloat162*>(p.bias + gcol + 2 * lane);
+            bias_s[2 * lane] = __bfloat162float(b2.x);
+            bias_s[2 * lane + 1] = __bfloat162float(b2.y);
           }
-        }
-        __syncwarp();  // bias_s visible to the whole warp
-
-        uint32_t packed[32];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float lo = __uint_as_float(v[h][j]);
-            float hi = __uint_as_float(v[h][j + 1]);
-            if (p.bias != nullptr) {
-              lo += bias_s[h * 32 + j];
-              hi += bias_s[h * 32 + j + 1];
-            }
-            const __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
-            packed[h * 16 + j / 2] = *reinterpret_cast<const uint32_t*>(&r);
-          }
-        }
-
-        // Staging buffer reuse: the store issued two sub-tiles ago must have
-        // finished reading shared memory.
-        if (lane == 0) bulk_wait_group_read<kEpiBufs - 1>();
-        __syncwarp();
-        uint8_t* buf = epi_buf0 + (store_it & 1u) * kEpiBufBytes;
-        // Row `lane` = 128 bytes = 8 chunks of 16 bytes, chunk j stored at
-        // position j ^ (lane & 7): the 128-byte swizzle the store map expects.
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint4 val = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2],
-                                       packed[4 * j + 3]);
-          *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = val;
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if constexpr (MODE == MODE_PEER_WRITE) {
-          // The slots may still be read by their owners (copy-out of the previous
-          // operation): the first store of this warp waits for their hand-off.
-          if (!handoff_checked) {
-            handoff_checked = true;
-            const bool handed = sync_wait_warp(p.sync, lane);
-            if (lane == 0) {
-              fence_proxy_async_all();  // the acquires above before the async-proxy stores below
-              if (!handed) *abort_flag = 1u;
-            }
+          uint32_t v[2][32];
+          const uint32_t taddr =
+              tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kBlockN + c * kEpiCols;
+          tmem_ld_32x32(taddr, v[0]);
+          tmem_ld_32x32(taddr + 32, v[1]);
+          tmem_ld_wait();
+          if (c == chunks - 1) {
+            // Accumulator fully read: hand the TMEM slot back to the MMA warp.
+            tc_fence_before_sync();
             __syncwarp();
-            if (!handed) {
-              ok = false;
-              break;
-            }
-          }
-        }
-        if (lane == 0) {
-          if (row0 < p.M && in_range) {
-            if constexpr (MODE == MODE_PEER_WRITE) {
-              const int dst = gcol / p.shard;
-              const int lcol = gcol - dst * p.shard;
-              if ((p.flags & kFlagNoL2Hints) == 0u) {
-                tma_store_2d_hint(&p.map_out[dst], lcol, row0, smem_u32(buf), l2_policy_evict_first());
+            if (lane == 0) {
+              if constexpr (G == 1) {
+                mbar_arrive(acc_empty_bar(as));
               } else {
-                tma_store_2d(&p.map_out[dst], lcol, row0, smem_u32(buf));
-              }
-            } else {
-              if ((p.flags & kFlagNoL2Hints) == 0u) {
-                tma_store_2d_hint(&p.map_out[0], gcol, row0, smem_u32(buf), l2_policy_evict_first());
-              } else {
-                tma_store_2d(&p.map_out[0], gcol, row0, smem_u32(buf));
+                mbar_arrive_cluster(acc_empty_leader0 + 8u * as);
               }
             }
           }
-          bulk_commit_group();
+          __syncwarp();  // bias_s visible to the whole warp
+
+          uint32_t packed[32];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float lo = __uint_as_float(v[h][j]);
+              float hi = __uint_as_float(v[h][j + 1]);
+              if (p.bias != nullptr) {
+                lo += bias_s[h * 32 + j];
+                hi += bias_s[h * 32 + j + 1];
+              }
+              const __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+              packed[h * 16 + j / 2] = *reinterpret_cast<const uint32_t*>(&r);
+            }
+          }
+
+          // Staging buffer reuse: the store issued two sub-tiles ago must have
+          // finished reading shared memory.
+          if (lane == 0) bulk_wait_group_read<kEpiBufs - 1>();
+          __syncwarp();
+          uint8_t* buf = epi_buf0 + (store_it & 1u) * kEpiBufBytes;
+          // Row `lane` = 128 bytes = 8 chunks of 16 bytes, chunk j stored at
+          // position j ^ (lane & 7): the 128-byte swizzle the store map expects.
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 val = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2],
+                                         packed[4 * j + 3]);
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = val;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if constexpr (MODE == MODE_PEER_WRITE) {
+            // The slots may still be read by their owners (copy-out of the previous
+            // operation): the first store of this warp waits for their hand-off.
+            if (!handoff_checked) {
+              handoff_checked = true;
+              const bool handed = sync_wait_warp(p.sync, lane);
+              if (lane == 0) {
+                fence_proxy_async_all();  // the acquires above before the async-proxy stores below
+                if (!handed) *abort_flag = 1u;
+              }
+              __syncwarp();
+              if (!handed) {
+                ok = false;
+                break;
+              }
+            }
+          }
+          if (lane == 0) {
+            if (row0 < p.M && in_range) {
+              if constexpr (MODE == MODE_PEER_WRITE) {
+                const int dst = gcol / p.shard;
+                const int lcol = gcol - dst * p.shard;
+                if ((p.flags & kFlagNoL2Hints) == 0u) {
+                  tma_store_2d_hint(&p.map_out[dst], lcol, row0, smem_u32(buf), l2_policy_evict_first());
+                } else {
+                  tma_store_2d(&p.map_out[dst], lcol, row0, smem_u32(buf));
+                }
+              } else {
+                if ((p.flags & kFlagNoL2Hints) == 0u) {
+                  tma_store_2d_hint(&p.map_out[0], gcol, row0, smem_u32(buf), l2_policy_evict_first());
+                } else {
+                  tma_store_2d(&p.map_out[0], gcol, row0, smem_u32(buf));
+                }
+              }
+            }
+            bulk_commit_group();
+          }
+          ++store_it;
+          __syncwarp();
         }
-        ++store_it;
-        __syncwarp();
+        part_col0 += w.part_cols[part];
       }
     }
     // Stores must have completed (not merely been read out of shared memory)
@@ -762,6 +873,8 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
             // start-up: the first panels gate every CTA, publish them at once
             publish(pending_panel);
             pending_panel = -1;
+            if (trace && tickets_done == 0 && warp == 6 && lane == 0)
+              trace[kTracePullFirstNs] = globaltimer_ns() - trace[kTraceNsStart];
           }
           ++tickets_done;
         }

@@ -407,6 +407,81 @@ __device__ __forceinline__ uint32_t umma_kstep4_probe_next(uint32_t d_tmem, uint
   return next_ready;
 }
 
+// The same step for an item of two parts: the A tile of the stage feeds two
+// accumulators (two W boxes, two instruction descriptors), eight MMAs between
+// the probe and the commit.
+template <int G>
+__device__ __forceinline__ uint32_t umma_kstep8_probe_next(uint32_t d_tmem0, uint32_t d_tmem1, uint64_t a_desc,
+                                                           uint64_t b_desc0, uint64_t b_desc1, uint32_t idesc0,
+                                                           uint32_t idesc1, uint32_t commit_bar,
+                                                           uint32_t next_full_bar, uint32_t next_parity) {
+  uint32_t next_ready;
+  if constexpr (G == 1) {
+    asm volatile(
+        "{\n"
+        ".reg .pred pn;\n"
+        ".reg .b64 a1, a2, a3, b1, b2, b3, c1, c2, c3;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 pn, [%9], %10;\n"
+        "add.u64 a1, %3, 2;\n"
+        "add.u64 a2, %3, 4;\n"
+        "add.u64 a3, %3, 6;\n"
+        "add.u64 b1, %4, 2;\n"
+        "add.u64 b2, %4, 4;\n"
+        "add.u64 b3, %4, 6;\n"
+        "add.u64 c1, %5, 2;\n"
+        "add.u64 c2, %5, 4;\n"
+        "add.u64 c3, %5, 6;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %3, %4, %6, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a1, b1, %6, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a2, b2, %6, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a3, b3, %6, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], %3, %5, %7, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], a1, c1, %7, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], a2, c2, %7, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], a3, c3, %7, 1;\n"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%8];\n"
+        "selp.u32 %0, 1, 0, pn;\n"
+        "}\n"
+        : "=r"(next_ready)
+        : "r"(d_tmem0), "r"(d_tmem1), "l"(a_desc), "l"(b_desc0), "l"(b_desc1), "r"(idesc0), "r"(idesc1),
+          "r"(commit_bar), "r"(next_full_bar), "r"(next_parity)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred pn;\n"
+        ".reg .b64 a1, a2, a3, b1, b2, b3, c1, c2, c3;\n"
+        ".reg .b16 both;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 pn, [%9], %10;\n"
+        "mov.b16 both, 3;\n"
+        "add.u64 a1, %3, 2;\n"
+        "add.u64 a2, %3, 4;\n"
+        "add.u64 a3, %3, 6;\n"
+        "add.u64 b1, %4, 2;\n"
+        "add.u64 b2, %4, 4;\n"
+        "add.u64 b3, %4, 6;\n"
+        "add.u64 c1, %5, 2;\n"
+        "add.u64 c2, %5, 4;\n"
+        "add.u64 c3, %5, 6;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %3, %4, %6, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], a1, b1, %6, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], a2, b2, %6, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], a3, b3, %6, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%2], %3, %5, %7, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%2], a1, c1, %7, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%2], a2, c2, %7, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%2], a3, c3, %7, 1;\n"
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], both;\n"
+        "selp.u32 %0, 1, 0, pn;\n"
+        "}\n"
+        : "=r"(next_ready)
+        : "r"(d_tmem0), "r"(d_tmem1), "l"(a_desc), "l"(b_desc0), "l"(b_desc1), "r"(idesc0), "r"(idesc1),
+          "r"(commit_bar), "r"(next_full_bar), "r"(next_parity)
+        : "memory");
+  }
+  return next_ready;
+}
+
 // 32 lanes x 32 consecutive FP32 columns: thread t of the warp receives row
 // (lane quarter base + t), registers = columns.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {

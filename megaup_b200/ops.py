@@ -1019,11 +1019,21 @@ class _PullBase:
     def __call__(self, head_x: Tensor, *, validate_group: bool = True) -> Tensor:
         self._validate_call(head_x, validate_group)
         with torch.no_grad(), self.runtime.lease():
-            if self.compiled.epoch >= self.compiled.workspace_epochs:
-                self.compiled.reset_workspace(torch.cuda.current_stream(self.runtime.device))
+            self._refresh_workspace()
             self._stage(head_x)
             self._launch()
         return self.output
+
+    def _refresh_workspace(self) -> None:
+        """Zero the pull counters when they are used up, and after any device-side
+        failure the runtime has reported (an aborted launch leaves the ticket
+        cursor and the ready counts out of step with the launch ordinal)."""
+
+        runtime = self.runtime
+        seen = getattr(self, "_failures_seen", 0)
+        if self.compiled.epoch >= self.compiled.workspace_epochs or seen != runtime.failure_count:
+            self.compiled.reset_workspace(torch.cuda.current_stream(runtime.device))
+            self._failures_seen = runtime.failure_count
 
 
 @dataclass
@@ -1326,8 +1336,7 @@ def emulated_pull(prepared: Sequence[_PullBase], head_xs: Sequence[Tensor]) -> l
         op._validate_call(head_x, False)
     with torch.no_grad():
         for op, head_x in zip(prepared, head_xs):
-            if op.compiled.epoch >= op.compiled.workspace_epochs:
-                op.compiled.reset_workspace(torch.cuda.current_stream(op.runtime.device))
+            op._refresh_workspace()
             op._stage(head_x)
         for op in prepared:
             op._launch()

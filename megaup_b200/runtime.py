@@ -46,13 +46,23 @@ SHARD_MULTIPLE = 128
 _CONTROL_BYTES = 4096
 _FLAG_TIMEOUT_NS = int(float(os.environ.get("MEGA_UP_FLAG_TIMEOUT_S", "30")) * 1e9)
 _KERNEL_TIMEOUT_NS = int(float(os.environ.get("MEGA_UP_KERNEL_TIMEOUT_S", "5")) * 1e9)
-# "1" folds the two slot hand-offs of an operation into its kernels instead of
-# launching two barrier kernels. Off by default: on 2 B200s the folded form
-# measured 181-185 us per peer-write call against 176-177 us with the two
-# stand-alone barrier kernels (pull: 198 against 197), because every block of
-# the copy kernel then polls system-scope flags and the GEMM's last CTA has
-# to collect all arrivals before the flags go out.
-_FUSED_SYNC = os.environ.get("MEGA_UP_FUSED_SYNC", "0") == "1"
+# The two slot hand-offs of an operation ride inside its kernels: every kernel
+# of an operation waits for the sync point before it (at its first access to
+# memory the hand-off protects) and its last CTA signals the next one, so an
+# operation is two launches and the "slots may be reused" hand-off is only
+# waited for by the next operation, deep inside its first kernel.
+# MEGA_UP_FUSED_SYNC=0 goes back to two stand-alone barrier kernels per
+# operation (the reference's protocol, runtime.py:264, :281, :415, :421 there).
+_FUSED_SYNC = os.environ.get("MEGA_UP_FUSED_SYNC", "1") == "1"
+
+
+def _wire_epoch(count: int) -> int:
+    """The 32-bit value a sync point travels as. 0 means "no wait / no signal"
+    in the kernels' hand-off description, so the sequence skips it when it
+    wraps; waits compare by signed distance, which the gap of one does not
+    disturb."""
+
+    return (count - 1) % 0xFFFFFFFF + 1 if count > 0 else 0
 
 
 def unsupported_shape_reason(width: int, up: int) -> str | None:
@@ -256,6 +266,9 @@ class MegaUPRuntime:
     _leased_stream: int | None = field(default=None, init=False, repr=False)
     _lease_lock: threading.Lock = field(default_factory=threading.Lock, init=False, repr=False)
     _completion_event: torch.cuda.Event | None = field(default=None, init=False, repr=False)
+    # device-side failures observed so far; pull executables compare it with the
+    # count they last saw and zero their counters after a failure
+    failure_count: int = field(default=0, init=False, repr=False)
 
     @property
     def shard_hidden(self) -> int:
@@ -301,8 +314,8 @@ class MegaUPRuntime:
             peer_flags=self._flag_array,
             up=self.up,
             rank=self.local_rank,
-            wait_epoch=self._epoch & 0xFFFFFFFF,
-            signal_epoch=(self._epoch + 1) & 0xFFFFFFFF,
+            wait_epoch=_wire_epoch(self._epoch),
+            signal_epoch=_wire_epoch(self._epoch + 1),
             done_counter=self._done_counter.data_ptr(),
             done_before=self._done_value,
             done_after=0,
@@ -334,13 +347,25 @@ class MegaUPRuntime:
         word = self._status.read()
         if word:
             self._status.clear()
-            raise RuntimeError(f"Mega-UP device-side failure: {_native.decode_status(word)}")
+            self.failure_count += 1
+            raise RuntimeError(
+                f"Mega-UP device-side failure: {_native.decode_status(word)}; the results of the "
+                "operations enqueued since the last check are invalid (the next operation resets "
+                "the pull counters)"
+            )
 
     @contextmanager
     def lease(self) -> Iterator["MegaUPRuntime"]:
         """Non-re-entrant use of the arena; consecutive operations may run on
-        different streams (reference: runtime.py:151-171)."""
+        different streams (reference: runtime.py:151-171).
 
+        The status word the kernels write when a bounded wait runs out is read
+        on entry and after the operation has been enqueued (a plain host load of
+        pinned memory, no synchronisation): a failure of an EARLIER operation
+        raises ``RuntimeError`` here, at the next operation, so that a caller who
+        never calls ``check_status()`` still hears of it."""
+
+        self.check_status()
         stream = torch.cuda.current_stream(self.device)
         with self._lease_lock:
             if self._leased:
@@ -354,6 +379,7 @@ class MegaUPRuntime:
         self._leased_stream = stream.cuda_stream
         try:
             yield self
+            self.check_status()
         finally:
             self._leased_stream = None
             done = torch.cuda.Event()
@@ -378,7 +404,7 @@ class MegaUPRuntime:
             _native.pointer_array(self._flag_addresses),
             self.up,
             self.local_rank,
-            self._epoch & 0xFFFFFFFF,
+            _wire_epoch(self._epoch),
             self.status_address,
             _FLAG_TIMEOUT_NS if timeout_s is None else int(timeout_s * 1e9),
             self._stream(),

@@ -127,3 +127,19 @@ def ulp_distance(a: torch.Tensor, b: torch.Tensor, floor: float = 2.0 ** -6) -> 
     scale = torch.maximum(torch.maximum(a32.abs(), b32.abs()), torch.full_like(a32, floor))
     ulp = torch.exp2(torch.floor(torch.log2(scale)) - 7)
     return float(((a32 - b32).abs() / ulp).max())
+
+
+def representation_ulps(a: torch.Tensor, b: torch.Tensor) -> int:
+    """Largest distance between two BF16 tensors counted in representable BF16
+    values (the true ulp count, no floor): the bit patterns are mapped to
+    integers that increase with the value, so neighbours differ by one whatever
+    their magnitude. A result that cancels to almost zero can be many such ulps
+    away from a differently ordered FP32 sum while being a tiny absolute error;
+    `ulp_distance` (with its floor) is the pass/fail measure for those."""
+
+    def ordered(t: torch.Tensor) -> torch.Tensor:
+        bits = t.contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+        negative = bits >= 0x8000
+        return torch.where(negative, 0x8000 - bits, bits)
+
+    return int((ordered(a.to(torch.bfloat16)) - ordered(b.to(torch.bfloat16))).abs().max())

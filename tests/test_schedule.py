@@ -1,0 +1,125 @@
+"""The work-item lists the library builds (host arithmetic, no GPU): every list
+must tile the output exactly once, respect the widest item a CTA grouping can
+run, and start every rank of a peer-write group in a different column block."""
+
+from __future__ import annotations
+
+import ctypes
+from collections import defaultdict
+
+import pytest
+
+from megaup_b200 import _native, build
+
+NO_ITEM = 0xFFFFFFFF
+UNIT = 64
+
+SHAPES = [
+    # rows, n, k, up
+    (4096, 5120, 5120, 8),     # Wan2.1-14B projection
+    (4096, 5120, 5120, 2),
+    (8192, 6144, 4096, 8),     # Llama-3-8B fused QKV
+    (16384, 8192, 8192, 8),    # Llama-3-70B O projection
+    (512, 2304, 2304, 2),      # odd number of 256-column blocks
+    (1024, 2048, 2048, 8),
+    (64, 1024, 4096, 8),       # fewer rows than a row tile
+    (300, 2304, 2304, 2),      # ragged rows
+    (65536, 5120, 5120, 8),
+    (129, 256, 64, 2),
+]
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _library() -> None:
+    build.ensure_built()
+
+
+def preview(mode: int, rows: int, n: int, k: int, up: int, rank: int, cta_group: int, slots: int):
+    count, widest, cycles = ctypes.c_int(), ctypes.c_int(), ctypes.c_double()
+    _native.call(
+        "mup_schedule_preview", mode, rows, n, k, up, rank, cta_group, slots, None, 0,
+        ctypes.byref(count), ctypes.byref(widest), ctypes.byref(cycles),
+    )
+    buffer = (ctypes.c_uint32 * max(1, count.value))()
+    _native.call(
+        "mup_schedule_preview", mode, rows, n, k, up, rank, cta_group, slots, buffer, count.value,
+        None, None, None,
+    )
+    return list(buffer[: count.value]), widest.value, cycles.value
+
+
+def decode(entry: int) -> tuple[int, int, int]:
+    return entry & 0x3FFF, (entry >> 14) & 0xFFF, ((entry >> 26) & 0x7) + 1
+
+
+@pytest.mark.parametrize("rows,n,k,up", SHAPES)
+@pytest.mark.parametrize("mode", (0, 1))
+@pytest.mark.parametrize("cta_group,slots", ((2, 74), (1, 148), (2, 8)))
+def test_items_tile_the_output_exactly_once(rows, n, k, up, mode, cta_group, slots) -> None:
+    items, widest, cycles = preview(mode, rows, n, k, up, up - 1, cta_group, slots)
+    m_tiles = -(-rows // (128 * cta_group))
+    covered: dict[int, list[tuple[int, int]]] = defaultdict(list)
+    limit = 512 if cta_group == 2 else 256
+    seen_widest = 0
+    for entry in items:
+        if entry == NO_ITEM:
+            continue
+        m, n0, w = decode(entry)
+        assert 0 <= m < m_tiles
+        assert UNIT * w <= limit
+        seen_widest = max(seen_widest, UNIT * w)
+        covered[m].append((n0, n0 + w))
+    assert seen_widest == widest
+    assert cycles > 0
+    assert sorted(covered) == list(range(m_tiles))
+    for m, spans in covered.items():
+        spans.sort()
+        assert spans[0][0] == 0 and spans[-1][1] == n // UNIT, (m, spans)
+        for (_, stop), (start, _) in zip(spans, spans[1:]):
+            assert stop == start, (m, spans)
+    # the list never ends in a placeholder, and placeholders only pad whole rounds
+    assert items[-1] != NO_ITEM
+    if NO_ITEM in items:
+        assert len(items) > slots
+
+
+def test_headline_shape_uses_wide_items_and_balances_the_rounds() -> None:
+    items, widest, _ = preview(0, 4096, 5120, 5120, 8, 0, 2, 74)
+    assert widest > 256  # items of two accumulators: one A tile feeds both
+    per_slot: dict[int, int] = defaultdict(int)
+    for index, entry in enumerate(items):
+        if entry != NO_ITEM:
+            per_slot[index % 74] += decode(entry)[2]
+    total = 16 * (5120 // UNIT)
+    assert sum(per_slot.values()) == total
+    # no CTA pair carries more than 64 columns above an even share
+    assert max(per_slot.values()) <= -(-total // 74) + 1
+
+
+def test_peer_write_ranks_start_in_different_column_blocks() -> None:
+    starts = []
+    for rank in range(8):
+        items, _, _ = preview(0, 4096, 5120, 5120, 8, rank, 2, 74)
+        starts.append(decode(items[0])[1] * UNIT)
+    assert starts[0] == 0
+    assert len(set(starts)) == 8
+    assert starts == sorted(starts)
+    # pull lists do not rotate: every rank consumes its panels from column 0
+    for rank in (0, 5):
+        items, _, _ = preview(1, 4096, 5120, 5120, 8, rank, 2, 74)
+        assert decode(items[0])[:2] == (0, 0)
+
+
+def test_pull_lists_consume_row_tiles_in_ascending_order_in_the_first_round() -> None:
+    items, _, _ = preview(1, 4096, 5120, 5120, 8, 3, 2, 74)
+    first_round = [decode(entry)[0] for entry in items[:74]]
+    assert first_round == sorted(first_round)
+
+
+def test_bad_schedule_arguments_are_rejected() -> None:
+    with pytest.raises(_native.NativeError):
+        preview(2, 4096, 5120, 5120, 8, 0, 2, 74)
+    with pytest.raises(_native.NativeError):
+        preview(0, 4096, 5000, 5120, 8, 0, 2, 74)
+    with pytest.raises(_native.NativeError):
+        preview(0, 4096, 5120, 5120, 8, 8, 2, 74)
