@@ -87,6 +87,15 @@ int mup_schedule_preview(int mode, int rows, int n, int k, int up, int rank, int
                          uint32_t *items, int capacity, int *count, int *max_item_cols,
                          double *model_cycles);
 
+/* Plans created by the calling thread after this call launch at most
+ * `max_ctas` CTAs (0 lifts the limit), leaving the other SMs to kernels of
+ * other streams. The kernels need their whole grid resident at once (the pull
+ * workers of every CTA own a share of the first tickets), so a caller that runs
+ * them next to other work reserves room this way. Plays the part of the
+ * `max_active_ctas` argument of the reference's compile_headshard_pull_gemm
+ * (mega_up/kernels/headshard_pull_gemm.py:2440-2777). */
+int mup_set_max_active_ctas(int max_ctas);
+
 /* ---- status word ---------------------------------------------------------- */
 
 /* One 64-byte block of pinned, device-mapped host memory. `host_ptr` is read
@@ -236,9 +245,9 @@ int mup_pull_plan_destroy(mup_pull_plan *plan);
  * Same computation as mup_pull_plan_create + mup_pull_launch: it fills `dy`
  * ([rows,k]) from the `up` staged peer arenas and writes
  * out = bf16(dy @ W^T + bias) to `out_buf` ([rows,n]); the caller still
- * passes every input and output. What differs is the scratch (ticket cursor
- * and per-panel ready counts): it is a fixed array inside the library's device
- * image, about 16 KB per GPU, held by every GPU that loads the library until
+ * passes every input and output. What differs is the scratch (ticket cursor,
+ * one claim word per pull warp and the per-panel ready counts): it is a fixed array inside the library's device
+ * image, about 24 KB per GPU, held by every GPU that loads the library until
  * the process exits. The call performs no cudaMalloc/cudaFree, creates no
  * plan object and calls no allocating library routine.
  *
@@ -277,6 +286,13 @@ int mup_gather_rows_synced(void *dst, const void *src, const int64_t *index, int
  * Replaces the permuted copy_ at mega_up/runtime.py:272-280 and :399-414. */
 int mup_regroup_rows(void *dst, const void *src, int up, int batch, int64_t seq,
                      int64_t row_elems, int to_batch_major, void *stream);
+
+/* Diagnostic (no counterpart in the reference): one thread issues `iters`
+ * dependent 8-byte loads from `zeros` (at least 2 KiB of zero-filled device
+ * memory, local or a mapped peer arena) and writes the elapsed nanoseconds to
+ * out_ns[0] (device memory): elapsed / iters is the load round-trip time, over
+ * NVLink when `zeros` belongs to a peer. */
+int mup_probe_load_latency(const void *zeros, int iters, uint64_t *out_ns, void *stream);
 
 /* mup_regroup_rows with the hand-off folded in (see mup_gather_rows_synced). */
 int mup_regroup_rows_synced(void *dst, const void *src, int up, int batch, int64_t seq,

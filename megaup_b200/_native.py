@@ -64,6 +64,7 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
             POINTER(c_int), POINTER(c_int), POINTER(ctypes.c_double),
         ),
     ),
+    "mup_set_max_active_ctas": (c_int, (c_int,)),
     "mup_status_create": (c_int, (POINTER(POINTER(c_uint32)), POINTER(c_void_p))),
     "mup_status_destroy": (c_int, (POINTER(c_uint32),)),
     "mup_arena_create": (c_int, (c_int, c_uint64, POINTER(c_void_p))),
@@ -124,6 +125,7 @@ SIGNATURES: dict[str, tuple[object, tuple[object, ...]]] = {
         c_int,
         (c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p, POINTER(MupSync)),
     ),
+    "mup_probe_load_latency": (c_int, (c_void_p, c_int, c_void_p, c_void_p)),
     "mup_regroup_rows": (
         c_int,
         (c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p),

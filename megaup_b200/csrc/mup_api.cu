@@ -201,6 +201,9 @@ int fill_sync(mup::SyncParams* sp, mup_sync* sync, unsigned long long participan
   return MUP_OK;
 }
 
+// Upper bound on the CTAs of plans created by this thread from now on (0: none).
+thread_local int g_max_ctas_option = 0;
+
 struct DeviceInfo {
   int sms = 0;
   int cc_major = 0;
@@ -560,6 +563,10 @@ int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int 
     slots = std::min(info.sms / 2, max_clusters);
     core->smem_bytes = mup::GemmCfg<2>::kSmemBytes;
   }
+  // A caller that shares the GPU with other kernels can leave SMs free: a grid
+  // that is not resident at once would stall at its first panel gates until
+  // the missing CTAs' pull warps get an SM.
+  if (g_max_ctas_option > 0) slots = std::max(1, std::min(slots, g_max_ctas_option / g));
   Schedule schedule = choose_schedule(MODE, m_tiles, n, p.k_tiles, up, rank, g, slots);
   const int clusters = static_cast<int>(std::min<size_t>(static_cast<size_t>(slots), schedule.items.size()));
   core->grid = clusters * g;
@@ -719,6 +726,20 @@ __global__ void regroup_rows_kernel(uint4* __restrict__ dst, const uint4* __rest
   }
 }
 
+// Round-trip time of dependent loads: every load's address depends on the value
+// before it (the buffer holds zeros), so the loads cannot overlap.
+__global__ void load_latency_kernel(const unsigned long long* __restrict__ ptr, int iters,
+                                    unsigned long long* __restrict__ out_ns) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const volatile unsigned long long* p = ptr;
+  unsigned long long offset = 0;
+  for (int i = 0; i < 16; ++i) offset = p[offset];  // warm the path (TLB, routing)
+  const uint64_t t0 = mup::globaltimer_ns();
+  for (int i = 0; i < iters; ++i) offset = p[offset + (static_cast<unsigned long long>(i) & 15ull) * 16ull];
+  const uint64_t t1 = mup::globaltimer_ns();
+  out_ns[0] = t1 - t0 + offset;  // offset is 0; keeps the chain alive
+}
+
 // The two copies with the hand-off folded in: every block waits (thread 0
 // polls this rank's flags) before it touches the slots, and counts itself in
 // after its last store; the last block raises the flags at the peers.
@@ -836,6 +857,12 @@ int mup_shape_rule(int64_t width, int up) { return shape_rule(width, up); }
 int mup_peer_n_rotation(int rank, int up, int n_total, int tile_n) {
   if (up <= 0 || n_total <= 0 || tile_n <= 0 || rank < 0) return 0;
   return n_rotation(rank, up, n_total, tile_n);
+}
+
+int mup_set_max_active_ctas(int max_ctas) {
+  if (max_ctas < 0) return fail(MUP_ERR_BAD_ARG, "max_ctas must be >= 0");
+  g_max_ctas_option = max_ctas;
+  return MUP_OK;
 }
 
 // ---------------------------------------------------------------- schedule preview
@@ -1152,8 +1179,9 @@ int mup_pull_ticket_shape(int shard_elems, int* rows, int* segments) {
 uint64_t mup_pull_workspace_bytes(int rows) {
   if (rows <= 0) return 0;
   const uint64_t panels = (static_cast<uint64_t>(rows) + mup::kBlockM - 1) / mup::kBlockM;
-  // [0] ticket cursor, [16 ..] per-panel ready counts (cursor on its own 128-byte line)
-  return (16 + panels) * sizeof(unsigned long long);
+  // [0] ticket cursor (on its own 128-byte line), [16 ..] one claim word per pull warp, then
+  // the per-panel ready counts
+  return (16 + mup::kPullClaimWords + panels) * sizeof(unsigned long long);
 }
 
 int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k, int up, int rank,
@@ -1186,7 +1214,8 @@ int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k
     p.peer_rows = peer_rows;
     unsigned long long* ws = static_cast<unsigned long long*>(workspace);
     p.cursor = ws;
-    p.ready = ws + 16;
+    p.claimed = ws + 16;
+    p.ready = ws + 16 + mup::kPullClaimWords;
     set_pull_geometry(p, rows);
     for (int i = 0; i < up && rc == MUP_OK; ++i) {
       if (peer_arena_ptrs[i] == nullptr || reinterpret_cast<uintptr_t>(peer_arena_ptrs[i]) % 16)
@@ -1201,6 +1230,7 @@ int mup_pull_plan_create(mup_pull_plan** out, int device, int rows, int n, int k
     plan->workspace_bytes = mup_pull_workspace_bytes(rows);
     plan->pull_warps = static_cast<unsigned long long>(plan->core.grid) * mup::kPullWarps;
     p.pull_stride = static_cast<int>(plan->pull_warps);
+    if (p.pull_stride > mup::kPullClaimWords) p.claimed = nullptr;  // more pull warps than claim words: no stealing
   }
   if (rc != MUP_OK) {
     delete plan;
@@ -1278,12 +1308,13 @@ int mup_pull_plan_destroy(mup_pull_plan* plan) {
 
 namespace {
 
-// Scratch of the allocation-free pull entry point: the ticket cursor (word 0)
-// and one ready count per 128-row panel (from word 16). It lives in the
+// Scratch of the allocation-free pull entry point: the ticket cursor (word 0),
+// one claim word per pull warp (from word 16) and one ready count per 128-row
+// panel behind them. It lives in the
 // library's device image, so every GPU that loads the library holds these
 // bytes until the process exits, and every call on a GPU shares them.
 constexpr int kNoAllocMaxRows = MUP_NOALLOC_MAX_ROWS;
-constexpr int kNoAllocScratchWords = 16 + kNoAllocMaxRows / mup::kBlockM;
+constexpr int kNoAllocScratchWords = 16 + mup::kPullClaimWords + kNoAllocMaxRows / mup::kBlockM;
 static __device__ __align__(256) unsigned long long g_noalloc_pull_scratch[kNoAllocScratchWords];
 
 constexpr int kNoAllocMaxDevices = 64;
@@ -1419,7 +1450,8 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
   p.dy = static_cast<__nv_bfloat16*>(dy);
   p.peer_rows = peer_rows;
   p.cursor = dev->scratch;
-  p.ready = dev->scratch + 16;
+  p.claimed = dev->scratch + 16;
+  p.ready = dev->scratch + 16 + mup::kPullClaimWords;
   p.epoch1 = 1;       // the scratch is cleared below, so every call is "the first launch"
   p.cursor_base = 0;
   set_pull_geometry(p, rows);
@@ -1436,11 +1468,12 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
   const int grid = (p.num_items < slots ? p.num_items : slots) * g;
 
   p.pull_stride = grid * mup::kPullWarps;
+  if (p.pull_stride > mup::kPullClaimWords) p.claimed = nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // The array keeps the previous call's counts: the cursor and the ready
   // counts of the panels this call uses must start at zero.
   const size_t panels = (static_cast<size_t>(rows) + mup::kBlockM - 1) / mup::kBlockM;
-  MUP_CUDA(cudaMemsetAsync(dev->scratch, 0, (16 + panels) * sizeof(unsigned long long), s));
+  MUP_CUDA(cudaMemsetAsync(dev->scratch, 0, (16 + mup::kPullClaimWords + panels) * sizeof(unsigned long long), s));
   return (g == 2) ? launch_kernel<2, mup::MODE_PULL>(p, grid, s)
                   : launch_kernel<1, mup::MODE_PULL>(p, grid, s);
 }
@@ -1491,6 +1524,17 @@ int mup_regroup_rows_synced(void* dst, const void* src, int up, int batch, int64
   MUP_CUDA(launch_small(regroup_rows_synced_kernel, grid, 256, static_cast<cudaStream_t>(stream),
                         static_cast<uint4*>(dst), static_cast<const uint4*>(src), up, batch, seq, vecs,
                         to_batch_major, sp));
+  return MUP_OK;
+}
+
+int mup_probe_load_latency(const void* zeros, int iters, uint64_t* out_ns, void* stream) {
+  if (zeros == nullptr || out_ns == nullptr || iters <= 0)
+    return fail(MUP_ERR_BAD_ARG, "bad latency probe arguments");
+  if (reinterpret_cast<uintptr_t>(zeros) % 8 || reinterpret_cast<uintptr_t>(out_ns) % 8)
+    return fail(MUP_ERR_BAD_ARG, "latency probe buffers must be 8-byte aligned");
+  load_latency_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned long long*>(zeros), iters, reinterpret_cast<unsigned long long*>(out_ns));
+  MUP_CUDA(cudaGetLastError());
   return MUP_OK;
 }
 

@@ -73,6 +73,7 @@ constexpr int kPullMaxVecs = MUP_PULL_MAX_VECS;  // 16-byte vectors per pull tic
 constexpr int kPullUnroll = kPullMaxVecs / 32;
 constexpr int kPullWarps = 6;         // pull workers per CTA (warps 6 .. 6 + kPullWarps - 1)
 constexpr int kPullChunk = 8;         // tickets drawn per atomic
+constexpr int kPullClaimWords = 1024; // one claim word per pull warp of the grid (148 SMs x 6 = 888)
 
 constexpr int MODE_PEER_WRITE = 0;
 constexpr int MODE_PULL = 1;
@@ -152,6 +153,7 @@ struct GemmParams {
   __nv_bfloat16* dy;                 // dense pulled input [M, K]
   unsigned long long* ready;         // [ceil(M/128)] monotonically increasing ticket counts
   unsigned long long* cursor;        // monotonically increasing cursor, in chunks of kPullChunk tickets
+  unsigned long long* claimed;       // [pull_stride] launch ordinal that claimed a pull warp's pre-assigned first chunk (nullptr: no stealing)
   unsigned long long epoch1;         // launch ordinal, 1-based
   unsigned long long cursor_base;    // cursor value that means "chunk 0" for this launch
   int peer_rows;
@@ -190,10 +192,13 @@ constexpr unsigned int kFlagSeparateIssue = 2u;  // tuning: poll, MMAs and commi
 constexpr unsigned int kFlagPullExtraFence = 16u;  // tuning: an explicit fence.acq_rel.gpu before every release of a ready count
 constexpr unsigned int kFlagNoWPrefetch = 32u;  // tuning: pull mode, do not load W ahead of a closed panel gate
 
+// The first role of a CTA that gives up records why; roles that give up because
+// the abort flag is already up leave the recorded cause alone.
 __device__ __forceinline__ void report_status(const GemmParams& p, volatile uint32_t* abort_flag,
                                               uint32_t code, uint32_t detail) {
+  const bool first = (*abort_flag == 0u);
   *abort_flag = 1u;
-  if (p.status != nullptr) {
+  if (first && p.status != nullptr) {
     *reinterpret_cast<volatile uint32_t*>(p.status) = (code << 24) | (detail & 0xFFFFFFu);
   }
 }
@@ -349,6 +354,17 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   if (trace != nullptr && threadIdx.x == 0) {
     trace[kTraceStart] = clock64();
     trace[kTraceNsStart] = globaltimer_ns();
+  }
+  // Pull mode: every pull warp claims its pre-assigned first chunk for this
+  // launch. The claim words only ever grow (launch ordinals), so the claim may
+  // be made before the previous launch of the plan has completed, and its
+  // latency hides behind the set-up below.
+  bool own_first_chunk = true;
+  if constexpr (MODE == MODE_PULL) {
+    if (warp >= 6 && lane == 0 && p.claimed != nullptr) {
+      const unsigned long long me = static_cast<unsigned long long>(blockIdx.x) * kPullWarps + (warp - 6);
+      own_first_chunk = atomicMax(p.claimed + me, p.epoch1) < p.epoch1;
+    }
   }
 
   // ------------------------------------------------------------------ set-up
@@ -848,37 +864,78 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       int pending_panel = -1;
       int tickets_done = 0;
-      // The first chunk of every pull warp is its own index (no atomic on the
-      // critical path of the first panels); the cursor hands out the rest.
-      unsigned long long c = static_cast<unsigned long long>(blockIdx.x) * kPullWarps + (warp - 6);
-      while (c < chunks && *abort_flag == 0u) {
+      // The first chunk of every pull warp is its own index (no cursor draw on the
+      // critical path of the first panels); the cursor hands out the rest. Once
+      // the cursor has run out, a warp looks for first chunks whose owner has
+      // not shown up (a CTA that could not become resident because another
+      // kernel holds its SM) and copies them in its place, so the CTAs that do
+      // run never wait on one that does not.
+      const unsigned long long me = static_cast<unsigned long long>(blockIdx.x) * kPullWarps + (warp - 6);
+      unsigned long long c = me;
+      bool copy_it = __shfl_sync(0xffffffffu, own_first_chunk ? 1 : 0, 0) != 0;
+      bool stealing = false;
+      unsigned long long steal_pos = 0;
+      while (*abort_flag == 0u) {
         // Draw the next chunk now but read the result only after this chunk: at
         // kernel start every pull warp of the grid hits the cursor at once and the
         // same-address atomics take ~8 ns each, up to 7 us for the last warp.
         unsigned long long drawn = 0;
-        if (lane == 0) drawn = atomicAdd(p.cursor, 1ull);
-        const unsigned long long t_first = (c / stride) * block + (c % stride);
-        for (int i = 0; i < kPullChunk; ++i) {
-          const unsigned long long t = t_first + static_cast<unsigned long long>(i) * stride;
-          if (t >= total) break;
-          const PullTicket k = pull_ticket_geometry(p, t);
-          const int panel = k.panel;
-          uint4 regs[kPullUnroll];
-          pull_ticket_load(p, k, lane, regs);
-          if (pending_panel >= 0) publish(pending_panel);
-          pull_ticket_store(p, k, lane, regs);
-          __syncwarp();
-          pending_panel = panel;
-          if (tickets_done < 2) {
-            // start-up: the first panels gate every CTA, publish them at once
-            publish(pending_panel);
-            pending_panel = -1;
-            if (trace && tickets_done == 0 && warp == 6 && lane == 0)
-              trace[kTracePullFirstNs] = globaltimer_ns() - trace[kTraceNsStart];
+        if (!stealing && lane == 0) drawn = atomicAdd(p.cursor, 1ull);
+        if (copy_it) {
+          const unsigned long long t_first = (c / stride) * block + (c % stride);
+          for (int i = 0; i < kPullChunk; ++i) {
+            const unsigned long long t = t_first + static_cast<unsigned long long>(i) * stride;
+            if (t >= total) break;
+            const PullTicket k = pull_ticket_geometry(p, t);
+            const int panel = k.panel;
+            uint4 regs[kPullUnroll];
+            pull_ticket_load(p, k, lane, regs);
+            if (pending_panel >= 0) publish(pending_panel);
+            pull_ticket_store(p, k, lane, regs);
+            __syncwarp();
+            pending_panel = panel;
+            if (tickets_done < 2) {
+              // start-up: the first panels gate every CTA, publish them at once
+              publish(pending_panel);
+              pending_panel = -1;
+              if (trace && tickets_done == 0 && warp == 6 && lane == 0)
+                trace[kTracePullFirstNs] = globaltimer_ns() - trace[kTraceNsStart];
+            }
+            ++tickets_done;
           }
-          ++tickets_done;
         }
-        c = __shfl_sync(0xffffffffu, drawn, 0) - p.cursor_base + stride;
+        if (!stealing) {
+          c = __shfl_sync(0xffffffffu, drawn, 0) - p.cursor_base + stride;
+          copy_it = true;
+          if (c >= chunks) {
+            if (p.claimed == nullptr) break;
+            stealing = true;
+          }
+        }
+        if (stealing) {
+          bool found = false;
+          while (steal_pos < stride && !found) {
+            const unsigned long long idx = steal_pos + static_cast<unsigned long long>(lane);
+            const unsigned long long j = (me + 1ull + idx) % stride;
+            const unsigned long long seen = (idx < stride) ? *reinterpret_cast<volatile unsigned long long*>(p.claimed + j)
+                                                           : p.epoch1;
+            uint32_t open = __ballot_sync(0xffffffffu, seen < p.epoch1);
+            while (open != 0u && !found) {
+              const int bit = __ffs(static_cast<int>(open)) - 1;
+              open &= open - 1u;
+              const unsigned long long jj = (me + 1ull + steal_pos + static_cast<unsigned long long>(bit)) % stride;
+              unsigned long long before = p.epoch1;
+              if (lane == 0) before = atomicMax(p.claimed + jj, p.epoch1);
+              if (__shfl_sync(0xffffffffu, before < p.epoch1 ? 1 : 0, 0) != 0) {
+                c = jj;
+                found = true;
+              }
+            }
+            if (open == 0u && !found) steal_pos += 32ull;
+          }
+          if (!found) break;
+          copy_it = true;
+        }
       }
       if (pending_panel >= 0) publish(pending_panel);
       // This warp will not read a peer arena again: once every pull warp of the

@@ -162,6 +162,9 @@ def compile_headshard_pull_gemm(
     peer_rows: int | None = None,
     enable_clc: bool = True,
     enable_bulk_pull: bool = True,
+    hidden: int | None = None,
+    max_active_ctas: int | None = None,
+    num_c_stages: int | None = None,
     cta_group: int = 0,
     status_address: int = 0,
     timeout_ns: int = 5_000_000_000,
@@ -172,12 +175,18 @@ def compile_headshard_pull_gemm(
     ``peer_addresses`` holds the base address of every rank's arena (a device
     uint64 tensor such as ``MegaUPRuntime.peer_address_table``, read back to
     the host here, or a sequence of ints). ``enable_clc`` and
-    ``enable_bulk_pull`` are accepted for signature compatibility; this
-    kernel has one scheduling and one pull strategy.
+    ``enable_bulk_pull`` and ``num_c_stages`` are accepted for signature
+    compatibility; this kernel has one scheduling and one pull strategy and
+    always two accumulator slots. ``hidden``, when given, must be the pulled
+    width K. ``max_active_ctas`` caps the grid so that the kernel stays fully
+    resident next to other streams' kernels (the reference's runner leaves 16
+    SMs free that way, tests/run_pull_gemm_contention.py:224-225 there).
     """
 
-    del enable_clc, enable_bulk_pull
+    del enable_clc, enable_bulk_pull, num_c_stages
     device = weight.device
+    if hidden is not None and int(hidden) != int(weight.shape[1]):
+        raise ValueError(f"hidden={hidden} must equal the weight's input width {int(weight.shape[1])}")
     if isinstance(peer_addresses, Tensor):
         addresses = [int(v) for v in peer_addresses.view(torch.int64).tolist()]
     else:
@@ -206,13 +215,17 @@ def compile_headshard_pull_gemm(
     if not cta_group:
         cta_group = int(os.environ.get("MEGA_UP_CTA_GROUP", "0"))
     plan = ctypes.c_void_p()
-    _native.call(
-        "mup_pull_plan_create", ctypes.byref(plan), device.index, rows, n, k, int(up), int(rank),
-        rows if peer_rows is None else int(peer_rows), weight.data_ptr(),
-        None if bias is None else bias.data_ptr(), _native.pointer_array(addresses),
-        dy.data_ptr(), out.data_ptr(), workspace.data_ptr(), int(cta_group),
-        status_address or None, int(timeout_ns),
-    )
+    _native.call("mup_set_max_active_ctas", int(max_active_ctas or 0))
+    try:
+        _native.call(
+            "mup_pull_plan_create", ctypes.byref(plan), device.index, rows, n, k, int(up), int(rank),
+            rows if peer_rows is None else int(peer_rows), weight.data_ptr(),
+            None if bias is None else bias.data_ptr(), _native.pointer_array(addresses),
+            dy.data_ptr(), out.data_ptr(), workspace.data_ptr(), int(cta_group),
+            status_address or None, int(timeout_ns),
+        )
+    finally:
+        _native.call("mup_set_max_active_ctas", 0)
     compiled = CompiledHeadShardPullGemm(
         plan, workspace, (weight, bias, out, dy), workspace_epochs, rows, int(rank), int(up)
     )

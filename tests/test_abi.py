@@ -44,7 +44,7 @@ def test_host_only_entry_points(library: ctypes.CDLL) -> None:
     assert library.mup_shape_rule(1920, 2) == 3
     assert library.mup_shape_rule(1536, 8) == 4
     assert [library.mup_peer_n_rotation(r, 8, 5120, 256) for r in range(8)] == [0, 3, 5, 8, 10, 13, 15, 18]
-    assert library.mup_pull_workspace_bytes(4096) == (16 + 32) * 8
+    assert library.mup_pull_workspace_bytes(4096) == (16 + 1024 + 32) * 8
     assert library.mup_pull_workspace_bytes(0) == 0
 
 

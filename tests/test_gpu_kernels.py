@@ -225,6 +225,53 @@ def test_a_flag_nobody_raises_times_out_and_the_context_survives() -> None:
     status.close()
 
 
+def test_a_pull_whose_hand_off_never_comes_gives_up_and_the_plan_recovers() -> None:
+    """The pull workers wait (bounded) for the peers' staging hand-off. Nobody
+    raises the flag here: the launch must end with the hand-off status code, and
+    after a plan reset the same plan must run bit-exactly."""
+
+    import ctypes
+
+    from megaup_b200 import _native
+
+    rows, n, k, up, rank = 300, 512, 1024, 2, 1
+    w, b = _weights(n, k, 91, False)
+    peers = [h.seeded((up, rows, k // up), 95 + p, ints=False) for p in range(up)]
+    dy = torch.full((rows, k), float("nan"), device=h.DEVICE, dtype=torch.bfloat16)
+    out = torch.full((rows, n), float("nan"), device=h.DEVICE, dtype=torch.bfloat16)
+    nbytes = int(_native.lib().mup_pull_workspace_bytes(rows))
+    workspace = torch.zeros((nbytes + 127) // 128 * 16, dtype=torch.int64, device=h.DEVICE)
+    status = h.StatusWord()
+    plan = ctypes.c_void_p()
+    _native.call(
+        "mup_pull_plan_create", ctypes.byref(plan), h.DEVICE.index, rows, n, k, up, rank, rows, w.data_ptr(),
+        b.data_ptr(), _native.pointer_array([p.data_ptr() for p in peers]), dy.data_ptr(), out.data_ptr(),
+        workspace.data_ptr(), 2, status.device, h.TIMEOUT_NS,
+    )
+    try:
+        flags = [torch.zeros(8, dtype=torch.int32, device=h.DEVICE) for _ in range(up)]
+        flag_array = _native.pointer_array([f.data_ptr() for f in flags])
+        sync = _native.MupSync(
+            peer_flags=flag_array, up=up, rank=rank, wait_epoch=1, signal_epoch=0, done_counter=None,
+            done_before=0, done_after=0, status_device_ptr=status.device, timeout_ns=20_000_000,
+        )
+        _native.call("mup_pull_launch_synced", plan, h.stream_handle(), ctypes.byref(sync))
+        torch.cuda.synchronize()
+        assert status.value >> 24 == 7, _native.decode_status(status.value)
+        # recover: clear the word, zero the counters, launch normally
+        status.host[0] = 0
+        _native.call("mup_pull_plan_reset", plan, h.stream_handle())
+        _native.call("mup_pull_launch", plan, h.stream_handle())
+        torch.cuda.synchronize()
+        assert status.value == 0, _native.decode_status(status.value)
+        want_dy = torch.cat([p[rank] for p in peers], dim=1)
+        assert torch.equal(dy, want_dy)
+        assert torch.equal(out, F.linear(want_dy, w, b))
+    finally:
+        _native.call("mup_pull_plan_destroy", plan)
+        status.close()
+
+
 def test_plan_creation_rejects_what_the_kernels_cannot_run() -> None:
     import ctypes
 

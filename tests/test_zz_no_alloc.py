@@ -29,7 +29,7 @@ pytestmark = pytest.mark.gpu
 MAX_ROWS = 262144  # MUP_NOALLOC_MAX_ROWS in include/megaup.h
 
 
-def _no_alloc_pull(peers, weight, bias, *, rank, cta_group, guard_rows=8):
+def _no_alloc_pull(peers, weight, bias, *, rank, cta_group, guard_rows=8, check_device_memory=False):
     up = len(peers)
     _, rows, shard = peers[0].shape
     n, k = weight.shape
@@ -39,14 +39,20 @@ def _no_alloc_pull(peers, weight, bias, *, rank, cta_group, guard_rows=8):
     # every buffer exists before the call; the call itself may not allocate
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated(h.DEVICE)
+    # torch's counter does not see a cudaMalloc made inside the library; the
+    # driver's free-memory figure does (checked once the one-time set-up of the
+    # first call on this device is behind us)
+    free_before, _ = torch.cuda.mem_get_info(h.DEVICE)
     _native.call(
-        "mup_pull_gemm_noalloc", 0, rows, n, k, up, rank, rows, weight.data_ptr(),
+        "mup_pull_gemm_noalloc", h.DEVICE.index, rows, n, k, up, rank, rows, weight.data_ptr(),
         None if bias is None else bias.data_ptr(),
         _native.pointer_array([p.data_ptr() for p in peers]), dy.data_ptr(), out.data_ptr(),
         cta_group, status.device, h.TIMEOUT_NS, h.stream_handle(),
     )
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated(h.DEVICE) == before
+    if check_device_memory:
+        assert torch.cuda.mem_get_info(h.DEVICE)[0] == free_before, "the call changed the device's free memory"
     assert status.value == 0, _native.decode_status(status.value)
     status.close()
     return dy, out[:rows], bool(torch.isnan(out[rows:]).all())
@@ -67,8 +73,22 @@ def test_two_calls_in_a_row_match_the_plan_entry_points(cta_group: int) -> None:
         assert torch.equal(dy, want_dy)
         assert torch.equal(out, want_out)  # same kernel, same inputs: bit-exact
     # and the very same call twice
-    dy2, out2, _ = _no_alloc_pull(peers, weight, bias, rank=rank, cta_group=cta_group)
+    dy2, out2, _ = _no_alloc_pull(peers, weight, bias, rank=rank, cta_group=cta_group, check_device_memory=True)
     assert torch.equal(dy2, want_dy) and torch.equal(out2, want_out)
+
+
+def test_a_call_for_another_device_than_the_current_one_is_rejected() -> None:
+    lib = _native.lib()
+    dummy = torch.zeros(8, device=h.DEVICE, dtype=torch.bfloat16)
+    peers = _native.pointer_array([dummy.data_ptr()] * 2)
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs a second device ordinal to name")
+    other = (h.DEVICE.index + 1) % torch.cuda.device_count()
+    code = lib.mup_pull_gemm_noalloc(
+        other, 64, 256, 256, 2, 0, 64, dummy.data_ptr(), None, peers, dummy.data_ptr(), dummy.data_ptr(),
+        0, None, 1000, None,
+    )
+    assert code == -1 and b"current device" in lib.mup_last_error()
 
 
 def test_sizes_beyond_the_built_in_scratch_are_rejected_with_a_clear_error() -> None:
@@ -76,7 +96,7 @@ def test_sizes_beyond_the_built_in_scratch_are_rejected_with_a_clear_error() -> 
     dummy = torch.zeros(8, device=h.DEVICE, dtype=torch.bfloat16)
     peers = _native.pointer_array([dummy.data_ptr()] * 2)
     code = lib.mup_pull_gemm_noalloc(
-        0, MAX_ROWS + 1, 256, 256, 2, 0, MAX_ROWS + 1, dummy.data_ptr(), None, peers,
+        h.DEVICE.index, MAX_ROWS + 1, 256, 256, 2, 0, MAX_ROWS + 1, dummy.data_ptr(), None, peers,
         dummy.data_ptr(), dummy.data_ptr(), 0, None, 1000, None,
     )
     assert code == -1
@@ -84,7 +104,7 @@ def test_sizes_beyond_the_built_in_scratch_are_rejected_with_a_clear_error() -> 
     assert "MUP_NOALLOC_MAX_ROWS" in message and str(MAX_ROWS) in message
     # other contract violations are rejected before anything is launched
     assert lib.mup_pull_gemm_noalloc(
-        0, 64, 256, 384, 2, 0, 64, dummy.data_ptr(), None, peers, dummy.data_ptr(), dummy.data_ptr(),
+        h.DEVICE.index, 64, 256, 384, 2, 0, 64, dummy.data_ptr(), None, peers, dummy.data_ptr(), dummy.data_ptr(),
         0, None, 1000, None,
     ) == -1
     torch.cuda.synchronize()
