@@ -65,7 +65,16 @@ def main() -> int:
 
         x = randn((rows, k))
         slots = [torch.full((rows, n // up), float("nan"), device=device, dtype=torch.bfloat16) for _ in range(up)]
-        launch = module.prepare_peer_write(x, weight, None, slots, bias=bias, local_rank=rank)
+        # the reference binds [1, rows, .] views (mega_up/ops.py:677-714 there)
+        bound = module.make_peer_write_launch(
+            weight.unsqueeze(0), None, tuple(slot.unsqueeze(0) for slot in slots), a_shape=(1, rows, k), bias=bias,
+            local_rank=rank,
+        )
+        x3d = x.unsqueeze(0)
+
+        def launch() -> None:
+            bound(x3d)
+
         launch()
         torch.cuda.synchronize(device)
         got = torch.cat(slots, dim=1)

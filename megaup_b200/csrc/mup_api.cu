@@ -159,6 +159,10 @@ void set_pull_geometry(mup::GemmParams& p, int rows) {
   p.pull_seg_vecs = (vec_per_row + p.pull_segs - 1) / p.pull_segs;
   const int groups = (rows + p.pull_rows - 1) / p.pull_rows;
   p.total_tickets = groups * p.up * p.pull_segs;
+  p.pull_up_shift = 0;
+  while ((1 << p.pull_up_shift) < p.up) ++p.pull_up_shift;
+  p.pull_panel_shift = 0;
+  while ((p.pull_rows << p.pull_panel_shift) < mup::kBlockM) ++p.pull_panel_shift;
 }
 
 int shape_rule(int64_t width, int up) {
@@ -341,27 +345,38 @@ int check_common(int device, int rows, int n, int k, int up, int rank, const voi
 // ---------------------------------------------------------------- schedule
 //
 // The output is cut into work items of 128*G rows by 64..512 columns; CTA
-// (pair) c runs items c, c + slots, ... of the list built here. The list is
-// chosen with a small time model of one K step of an item of `cols` columns:
+// (pair) c runs items c, c + slots, ... of the list built here. Candidate lists
+// are rated with a time model calibrated on B200 (SM cycles at 1.6-1.7 GHz,
+// 4096 x 5120 x 5120, CTA pairs). One K step of an item of `cols` columns costs
 //
-//   tensor pipe   2 * cols cycles (128 x cols x 64 MACs per SM at 8192 FLOP/cycle)
-//   operand port  (128 + cols / G) rows * 128 bytes / port_bytes_per_cycle
+//   max(2 * cols, (3000 + 2 * cols) / stages)
 //
-// Measured on B200: 128-, 192- and 256-wide tiles all moved 11-12 TB/s from L2
-// to the SMs and took 206 / 162 / 149 us for 4096 x 5120 x 5120; inside the K
-// loop that is about 60 bytes per SM cycle, i.e. the port bounds every tile of
-// at most 256 columns while items of 384 columns and more (53 bytes per cycle
-// and less at full tensor rate) are bounded by the tensor pipe. For a number of rounds r the model spreads
-// r * slots items over the M tiles (rows of items differ by at most one item,
-// the items of a row by at most 64 columns), simulates the round-robin
-// assignment and keeps the list with the shortest critical path. Inside every
-// round after the first the items are then dealt so that the CTA (pair) with
-// the most work so far receives the cheapest item (`kNoItem` entries mark the
-// CTA pairs that sit out a partly filled last round).
+// : the tensor pipe needs 2 * cols cycles, and a stage is refilled only about
+// 3000 cycles after the MMAs released it (1.8 us: every K step touches lines no
+// SM has read in this round, so a stage completes at DRAM latency), which the
+// stages in flight cover only partly (measured per K step: 128-wide 410 with 8
+// stages, 192-wide 530 with 7, 256-wide 565-585 with 6). An item costs 1200
+// cycles on top (pipeline fill, accumulator hand-over); an item of two
+// accumulators (wider than 256 columns) 6500, because all of TMEM belongs to it
+// and the K loop of the next item cannot start before the epilogue has read an
+// accumulator; a change of stage geometry between two items of a CTA costs
+// another 3000.
+// Candidates: every M tile cut into q equal items, for a range of q; lists of
+// r * slots items for a few r, where the M tiles differ by at most one item; and
+// each of those with the items of a partly filled last round cut into f pieces
+// (f * leftover <= slots), which keeps more SMs busy at the end. The candidate
+// with the shortest critical path under round-robin assignment wins. Inside
+// every round after the first the items are then dealt so that the CTA (pair)
+// with the most work so far receives the cheapest item (`kNoItem` entries mark
+// the pairs that sit out a partly filled last round).
+// Measured and rejected: asking L2 for the boxes of later K steps with
+// cp.async.bulk.prefetch.tensor from the TMA producer, 4 to 24 K steps ahead,
+// by every CTA or by one CTA per line: the kernel went from 151 to 196-207 us
+// (the MMA warp then waits for operands 3.5 times as long).
 // Tuning overrides (environment): MEGA_UP_ITEM_UNITS=u forces items of u*64
-// columns, MEGA_UP_ROUNDS=r forces the number of rounds, MEGA_UP_BAND=b lists
-// the items of b consecutive M tiles column by column (peer-write only),
-// MEGA_UP_PORT_BPC sets the port term of the model.
+// columns, MEGA_UP_ROUNDS=r forces the number of rounds, MEGA_UP_SPLIT_TAIL=0
+// keeps the last round whole, MEGA_UP_BAND=b lists the items of b consecutive
+// M tiles column by column (peer-write only).
 
 int env_int(const char* name, int fallback) {
   const char* env = getenv(name);
@@ -374,21 +389,21 @@ struct Schedule {
   double critical_cycles = 0;
 };
 
-double model_port_bytes_per_cycle() {
-  if (const char* env = getenv("MEGA_UP_PORT_BPC")) {
-    const double v = atof(env);
-    if (v > 1.0) return v;
-  }
-  return 60.0;
+// Load latency the stages in flight have to cover, in SM cycles (about 1.8 us:
+// every K step touches lines no SM has read in this round of items).
+constexpr double kModelLoadLatency = 3000.0;
+
+double item_cycles(int units, int k_tiles, int g) {
+  const int cols = units * mup::kUnit;
+  const double tensor = 2.0 * cols;
+  const int stages = mup::tile_stages(mup::stage_class_cols(cols), g);
+  const double step = std::max(tensor, (kModelLoadLatency + tensor) / stages);
+  const double fixed = cols > mup::kBlockN ? 6500.0 : 1200.0;
+  return k_tiles * step + fixed;
 }
 
-double item_cycles(int units, int k_tiles, int g, double port_bpc) {
-  const double cols = units * static_cast<double>(mup::kUnit);
-  const double tensor = 2.0 * cols;
-  const double port = (mup::kBlockM + cols / g) * 128.0 / port_bpc;
-  // per item: the accumulator hand-over of its parts and the fill of the pipeline
-  const double fixed = units * mup::kUnit > mup::kBlockN ? 2500.0 : 1200.0;
-  return k_tiles * std::max(tensor, port) + fixed;
+int item_stage_class(uint32_t e) {
+  return mup::stage_class_cols((static_cast<int>((e >> 26) & 0x7u) + 1) * mup::kUnit);
 }
 
 // Items of one M tile: `q` items covering `units` 64-column units, the first
@@ -403,14 +418,23 @@ void emit_row(std::vector<uint32_t>* out, int m_idx, int units, int q, int start
   }
 }
 
-double list_item_cycles(uint32_t e, int k_tiles, int g, double port_bpc) {
+double list_item_cycles(uint32_t e, int k_tiles, int g) {
   if (e == mup::kNoItem) return 0.0;
-  return item_cycles(static_cast<int>((e >> 26) & 0x7u) + 1, k_tiles, g, port_bpc);
+  return item_cycles(static_cast<int>((e >> 26) & 0x7u) + 1, k_tiles, g);
 }
 
-double critical_path(const std::vector<uint32_t>& items, int slots, int k_tiles, int g, double port_bpc) {
+double critical_path(const std::vector<uint32_t>& items, int slots, int k_tiles, int g) {
   std::vector<double> load(static_cast<size_t>(slots), 0.0);
-  for (size_t i = 0; i < items.size(); ++i) load[i % slots] += list_item_cycles(items[i], k_tiles, g, port_bpc);
+  std::vector<int> last_class(static_cast<size_t>(slots), 0);
+  for (size_t i = 0; i < items.size(); ++i) {
+    if (items[i] == mup::kNoItem) continue;
+    const size_t c = i % static_cast<size_t>(slots);
+    load[c] += list_item_cycles(items[i], k_tiles, g);
+    // a change of stage geometry between two items drains the pipeline once
+    const int cls = item_stage_class(items[i]);
+    if (last_class[c] != 0 && last_class[c] != cls) load[c] += kModelLoadLatency;
+    last_class[c] = cls;
+  }
   return *std::max_element(load.begin(), load.end());
 }
 
@@ -418,10 +442,19 @@ double critical_path(const std::vector<uint32_t>& items, int slots, int k_tiles,
 // work so far gets the cheapest item of the round; a partly filled last round
 // goes to the least loaded slots and the others get kNoItem. The first round
 // keeps list order (in pull mode its items are the first panels to arrive).
-void balance_rounds(std::vector<uint32_t>* items, int slots, int k_tiles, int g, double port_bpc) {
+void balance_rounds(std::vector<uint32_t>* items, int slots, int k_tiles, int g, double start_cycles_per_m_tile) {
   const size_t n = items->size();
   if (n <= static_cast<size_t>(slots)) return;
   std::vector<double> load(static_cast<size_t>(slots), 0.0);
+  // Pull mode: a CTA pair cannot start before the rows of its first item have
+  // arrived, and rows arrive in ascending order at the rate the peers deliver
+  // them, so the pairs that start on later rows begin with that much "work".
+  if (start_cycles_per_m_tile > 0.0) {
+    for (int c = 0; c < slots; ++c) {
+      const uint32_t e = (*items)[static_cast<size_t>(c)];
+      if (e != mup::kNoItem) load[static_cast<size_t>(c)] = start_cycles_per_m_tile * ((e & 0x3FFFu) + 1u);
+    }
+  }
   std::vector<uint32_t> out;
   out.reserve((n + slots - 1) / slots * slots);
   for (size_t r0 = 0; r0 < n; r0 += slots) {
@@ -438,14 +471,14 @@ void balance_rounds(std::vector<uint32_t>* items, int slots, int k_tiles, int g,
                        [&](int a, int b) { return load[static_cast<size_t>(a)] > load[static_cast<size_t>(b)]; });
       // cheapest item first; ties keep list order
       std::stable_sort(round.begin(), round.end(), [&](uint32_t a, uint32_t b) {
-        return list_item_cycles(a, k_tiles, g, port_bpc) < list_item_cycles(b, k_tiles, g, port_bpc);
+        return list_item_cycles(a, k_tiles, g) < list_item_cycles(b, k_tiles, g);
       });
       // with fewer items than slots the most loaded slots sit the round out
       const size_t skip = static_cast<size_t>(slots) - count;
       for (size_t i = 0; i < count; ++i) placed[static_cast<size_t>(order[skip + i])] = round[i];
     }
     for (int c = 0; c < slots; ++c) {
-      load[static_cast<size_t>(c)] += list_item_cycles(placed[static_cast<size_t>(c)], k_tiles, g, port_bpc);
+      load[static_cast<size_t>(c)] += list_item_cycles(placed[static_cast<size_t>(c)], k_tiles, g);
       out.push_back(placed[static_cast<size_t>(c)]);
     }
   }
@@ -453,23 +486,52 @@ void balance_rounds(std::vector<uint32_t>* items, int slots, int k_tiles, int g,
   items->swap(out);
 }
 
-// q_of_row[m] items for M tile m.
-Schedule build_list(const std::vector<int>& q_of_row, int units, int up, int rank, bool rotate, int band,
-                    int slots, int k_tiles, int g, double port_bpc) {
+struct ListOptions {
+  int units = 0;  // 64-column units per M tile
+  int up = 1, rank = 0;
+  bool rotate = false;  // peer-write: each rank starts every M tile at its own column block
+  int band = 1;
+  int slots = 1;
+  int k_tiles = 1;
+  int g = 2;
+  double start_cycles_per_m_tile = 0.0;
+};
+
+// Cut every item of a partly filled last round into `pieces` narrower items (as
+// equal as 64-column units allow), so that the round keeps more SMs busy.
+void split_last_round(std::vector<uint32_t>* items, int slots, int pieces) {
+  const size_t leftover = items->size() % static_cast<size_t>(slots);
+  if (pieces < 2 || leftover == 0 || leftover * pieces > static_cast<size_t>(slots)) return;
+  std::vector<uint32_t> tail(items->end() - static_cast<long>(leftover), items->end());
+  items->resize(items->size() - leftover);
+  for (uint32_t e : tail) {
+    const int m = static_cast<int>(e & 0x3FFFu), n0 = static_cast<int>((e >> 14) & 0xFFFu);
+    const int w = static_cast<int>((e >> 26) & 0x7u) + 1;
+    const int f = std::min(pieces, w);
+    int at = n0;
+    for (int j = 0; j < f; ++j) {
+      const int piece = w / f + (j < w % f ? 1 : 0);
+      items->push_back(mup::encode_item(m, at, piece));
+      at += piece;
+    }
+  }
+}
+
+// q_of_row[m] items for M tile m; the last round's items cut into `tail_pieces`.
+Schedule build_list(const std::vector<int>& q_of_row, const ListOptions& o, int tail_pieces) {
   Schedule s;
   const int m_tiles = static_cast<int>(q_of_row.size());
   std::vector<std::vector<uint32_t>> rows(static_cast<size_t>(m_tiles));
   for (int m = 0; m < m_tiles; ++m) {
     const int q = q_of_row[m];
-    const int start = rotate ? ((rank * q + up - 1) / up) % q : 0;
-    emit_row(&rows[m], m, units, q, start);
-    s.max_cols = std::max(s.max_cols, ((units + q - 1) / q) * mup::kUnit);
+    const int start = o.rotate ? ((o.rank * q + o.up - 1) / o.up) % q : 0;
+    emit_row(&rows[m], m, o.units, q, start);
   }
-  if (band <= 1) {
+  if (o.band <= 1) {
     for (int m = 0; m < m_tiles; ++m) s.items.insert(s.items.end(), rows[m].begin(), rows[m].end());
   } else {
-    for (int m0 = 0; m0 < m_tiles; m0 += band) {
-      const int m1 = std::min(m_tiles, m0 + band);
+    for (int m0 = 0; m0 < m_tiles; m0 += o.band) {
+      const int m1 = std::min(m_tiles, m0 + o.band);
       size_t longest = 0;
       for (int m = m0; m < m1; ++m) longest = std::max(longest, rows[m].size());
       for (size_t j = 0; j < longest; ++j)
@@ -477,26 +539,40 @@ Schedule build_list(const std::vector<int>& q_of_row, int units, int up, int ran
           if (j < rows[m].size()) s.items.push_back(rows[m][j]);
     }
   }
-  if (env_int("MEGA_UP_BALANCE", 1) != 0) balance_rounds(&s.items, slots, k_tiles, g, port_bpc);
-  s.critical_cycles = critical_path(s.items, slots, k_tiles, g, port_bpc);
+  split_last_round(&s.items, o.slots, tail_pieces);
+  s.max_cols = 0;
+  for (uint32_t e : s.items) s.max_cols = std::max(s.max_cols, (static_cast<int>((e >> 26) & 0x7u) + 1) * mup::kUnit);
+  if (env_int("MEGA_UP_BALANCE", 1) != 0)
+    balance_rounds(&s.items, o.slots, o.k_tiles, o.g, o.start_cycles_per_m_tile);
+  s.critical_cycles = critical_path(s.items, o.slots, o.k_tiles, o.g);
   return s;
 }
 
 Schedule choose_schedule(int mode, int m_tiles, int n, int k_tiles, int up, int rank, int g, int slots) {
-  const int units = n / mup::kUnit;
+  ListOptions o;
+  o.units = n / mup::kUnit;
+  o.up = up;
+  o.rank = rank;
+  o.rotate = (mode == mup::MODE_PEER_WRITE);
+  o.band = o.rotate ? std::max(1, env_int("MEGA_UP_BAND", 1)) : 1;
+  o.slots = slots;
+  o.k_tiles = k_tiles;
+  o.g = g;
+  const int units = o.units;
   const int max_units = mup::max_item_cols(g) / mup::kUnit;
   const int q_min = (units + max_units - 1) / max_units;
-  const bool rotate = (mode == mup::MODE_PEER_WRITE);
-  const int band = rotate ? std::max(1, env_int("MEGA_UP_BAND", 1)) : 1;
-  const double port_bpc = model_port_bytes_per_cycle();
-  auto uniform = [&](int q) {
-    return build_list(std::vector<int>(static_cast<size_t>(m_tiles), q), units, up, rank, rotate, band, slots,
-                      k_tiles, g, port_bpc);
-  };
-  const int forced_units = env_int("MEGA_UP_ITEM_UNITS", 0);
-  if (forced_units >= 1 && forced_units <= max_units) {
-    return uniform(std::min(units, (units + forced_units - 1) / forced_units));
+  // Pull mode: SM cycles until one more M tile of rows has been pulled. The
+  // remote share of a tile's bytes at the rate peer loads deliver over NVLink
+  // (about 600 GB/s of the 770 GB/s a peer copy measures = 380 bytes per SM
+  // cycle at 1.6 GHz; MEGA_UP_PULL_BPC overrides, 0 ignores the start-up skew).
+  if (mode == mup::MODE_PULL && up > 1) {
+    double pull_bpc = 380.0;
+    if (const char* env = getenv("MEGA_UP_PULL_BPC")) pull_bpc = atof(env);
+    if (pull_bpc > 0.0)
+      o.start_cycles_per_m_tile =
+          static_cast<double>(mup::kBlockM) * g * k_tiles * mup::kBlockK * 2.0 * (up - 1) / up / pull_bpc;
   }
+  const bool may_split = env_int("MEGA_UP_SPLIT_TAIL", 1) != 0;
   Schedule best;
   bool have = false;
   auto consider = [&](Schedule&& cand) {
@@ -506,7 +582,27 @@ Schedule choose_schedule(int mode, int m_tiles, int n, int k_tiles, int up, int 
       have = true;
     }
   };
+  // a list as it is, and with its last round cut into 2, 3 and 4 pieces per item
+  auto consider_with_tails = [&](const std::vector<int>& q_of_row) {
+    consider(build_list(q_of_row, o, 1));
+    long long total = 0;
+    for (int q : q_of_row) total += q;
+    const long long leftover = total % slots;
+    if (!may_split || leftover == 0) return;
+    for (int pieces = 2; pieces <= 4 && leftover * pieces <= slots; ++pieces)
+      consider(build_list(q_of_row, o, pieces));
+  };
+  auto uniform = [&](int q) { return std::vector<int>(static_cast<size_t>(m_tiles), q); };
+  const int forced_units = env_int("MEGA_UP_ITEM_UNITS", 0);
+  if (forced_units >= 1 && forced_units <= max_units) {
+    consider_with_tails(uniform(std::min(units, (units + forced_units - 1) / forced_units)));
+    return best;
+  }
   const int forced_rounds = env_int("MEGA_UP_ROUNDS", 0);
+  if (forced_rounds <= 0) {
+    const int q_hi = std::min(units, q_min + 24);
+    for (int q = q_min; q <= q_hi; ++q) consider_with_tails(uniform(q));
+  }
   const long long min_items = static_cast<long long>(m_tiles) * q_min;
   const int r_lo = forced_rounds > 0 ? forced_rounds : static_cast<int>((min_items + slots - 1) / slots);
   const int r_hi = forced_rounds > 0 ? forced_rounds : r_lo + 3;
@@ -524,8 +620,7 @@ Schedule choose_schedule(int mode, int m_tiles, int n, int k_tiles, int up, int 
     }
     std::vector<int> q_of_row(static_cast<size_t>(m_tiles), static_cast<int>(q_lo));
     for (long long m = 0; m < rows_hi; ++m) q_of_row[static_cast<size_t>(m)] = static_cast<int>(q_lo + 1);
-    consider(build_list(q_of_row, units, up, rank, rotate, band, slots, k_tiles, g, port_bpc));
-    if (rows_hi != 0) consider(uniform(static_cast<int>(q_lo)));
+    consider_with_tails(q_of_row);
     if (q_lo >= units) break;
   }
   return best;
@@ -1426,12 +1521,11 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
     const int units = n / mup::kUnit;
     const int max_units = mup::max_item_cols(g) / mup::kUnit;
     const int q_min = (units + max_units - 1) / max_units;
-    const double port_bpc = model_port_bytes_per_cycle();
     int best_q = q_min;
     double best_cost = -1.0;
     for (int q = q_min; q <= units; ++q) {
       const long long rounds = (static_cast<long long>(m_tiles) * q + slots - 1) / slots;
-      const double cost = rounds * item_cycles((units + q - 1) / q, p.k_tiles, g, port_bpc);
+      const double cost = rounds * item_cycles((units + q - 1) / q, p.k_tiles, g);
       if (best_cost < 0.0 || cost < best_cost * 0.999) {
         best_cost = cost;
         best_q = q;

@@ -121,6 +121,18 @@ __host__ __device__ constexpr int tile_stages(int cols, int g) {
              : kStageAreaBytes / tile_stage_bytes(cols, g);
 }
 
+// Stage geometry is chosen per item from three classes, by the item's width: up
+// to 128 columns (8 stages of 24 KiB for a CTA pair), up to 256 (6 of 32 KiB)
+// and up to 512 (4 of 48 KiB). Narrow items (the cut-up last round of a list)
+// thus keep as many K steps in flight as the stage area allows, whatever the
+// widest item of the launch is. When consecutive items of a CTA differ in class
+// the TMA producer lets the pipeline drain (every stage consumed) and both
+// sides restart at stage 0; which phase of a stage's barriers comes next is
+// kept per stage, one bit each, so the ring may change its length.
+__host__ __device__ constexpr int stage_class_cols(int cols) {
+  return cols <= 2 * kUnit ? 2 * kUnit : (cols <= kBlockN ? kBlockN : kMaxItemUnits * kUnit);
+}
+
 // A work item as the host lists it: 14 bits M tile, 12 bits first column / 64, 3 bits (columns / 64 - 1).
 __host__ __device__ constexpr uint32_t encode_item(int m_idx, int n0_units, int w_units) {
   return static_cast<uint32_t>(m_idx) | (static_cast<uint32_t>(n0_units) << 14) |
@@ -162,6 +174,8 @@ struct GemmParams {
   int pull_rows;                     // rows per pull ticket: a power of two <= 16 with pull_rows * shard / 8 <= kPullMaxVecs
   int pull_segs;                     // column segments per shard row (> 1 only when one row exceeds a ticket; then pull_rows = 1)
   int pull_seg_vecs;                 // 16-byte vectors per segment
+  int pull_up_shift;                 // log2(up)
+  int pull_panel_shift;              // log2(128 / pull_rows)
   unsigned int flags;                // tuning switches (kFlag*)
   unsigned long long* trace;         // optional [grid][16] cycle counters (nullptr: off)
   SyncParams sync;                   // slot hand-off folded into this launch (flags[0] == nullptr: none)
@@ -215,13 +229,24 @@ struct PullTicket {
   int panel;  // the 128-row panel the ticket belongs to
 };
 
-__device__ __forceinline__ PullTicket pull_ticket_geometry(const GemmParams& p, unsigned long long t) {
+// Ticket numbers fit 32 bits (the host checks). With one segment per shard row
+// (shards of at most 4096 columns, the common case) a row group holds `up`
+// tickets and up is a power of two, so the split is a shift and a mask.
+__device__ __forceinline__ PullTicket pull_ticket_geometry(const GemmParams& p, uint32_t t) {
   const int vec_per_row = p.shard >> 3;
-  const unsigned long long per_group = static_cast<unsigned long long>(p.up) * p.pull_segs;
-  const int grp = static_cast<int>(t / per_group);
-  const int within = static_cast<int>(t - static_cast<unsigned long long>(grp) * per_group);
-  const int seg = within % p.pull_segs;
-  int src_rank = within / p.pull_segs + p.rank + 1;
+  int grp, seg, hop;
+  if (p.pull_segs == 1) {
+    grp = static_cast<int>(t >> p.pull_up_shift);
+    hop = static_cast<int>(t & static_cast<uint32_t>(p.up - 1));
+    seg = 0;
+  } else {
+    const uint32_t per_group = static_cast<uint32_t>(p.up * p.pull_segs);
+    grp = static_cast<int>(t / per_group);
+    const int within = static_cast<int>(t - static_cast<uint32_t>(grp) * per_group);
+    hop = within / p.pull_segs;
+    seg = within - hop * p.pull_segs;
+  }
+  int src_rank = hop + p.rank + 1;
   if (src_rank >= p.up) src_rank -= p.up;
   const int r0 = grp * p.pull_rows;
   int nrows = p.M - r0;
@@ -236,34 +261,41 @@ __device__ __forceinline__ PullTicket pull_ticket_geometry(const GemmParams& p, 
   }
   k.src = p.peers[src_rank] + (static_cast<size_t>(p.rank) * p.peer_rows + r0) * static_cast<size_t>(p.shard) + v0 * 8;
   k.dst = p.dy + static_cast<size_t>(r0) * p.K + static_cast<size_t>(src_rank) * p.shard + v0 * 8;
-  k.panel = grp / (kBlockM / p.pull_rows);
+  k.panel = grp >> p.pull_panel_shift;  // pull_rows is a power of two: 128 / pull_rows groups per panel
   return k;
 }
 
-__device__ __forceinline__ void pull_ticket_load(const GemmParams& p, const PullTicket& k, int lane,
-                                                 uint4 (&regs)[kPullUnroll]) {
-  const int vec_per_row = p.shard >> 3;
+// The rows of a ticket follow each other in the peer's staged shard, so lane l's
+// u-th vector is simply vector u * 32 + l of a contiguous block.
+__device__ __forceinline__ void pull_ticket_load(const PullTicket& k, int lane, uint4 (&regs)[kPullUnroll]) {
 #pragma unroll
   for (int u = 0; u < kPullUnroll; ++u) {
     const int vidx = u * 32 + lane;
-    if (vidx < k.nvec) {
-      const int rr = vidx / vec_per_row;
-      const int cc = vidx - rr * vec_per_row;
-      regs[u] = ld_stream_v4(k.src + static_cast<size_t>(rr) * p.shard + cc * 8);
-    }
+    if (vidx < k.nvec) regs[u] = ld_stream_v4(k.src + static_cast<size_t>(vidx) * 8);
   }
 }
 
-__device__ __forceinline__ void pull_ticket_store(const GemmParams& p, const PullTicket& k, int lane,
-                                                  const uint4 (&regs)[kPullUnroll]) {
+// In dy the rows are K elements apart. (row, column vector) of lane l's first
+// vector is the same for every ticket (`row0`, `vec0`, computed once per
+// kernel); each further vector lies 32 vectors on, which wraps into the next
+// row at most twice (a shard row has at least 16 vectors).
+__device__ __forceinline__ void pull_ticket_store(const GemmParams& p, const PullTicket& k, int lane, int row0,
+                                                  int vec0, const uint4 (&regs)[kPullUnroll]) {
   const int vec_per_row = p.shard >> 3;
+  int cc = vec0;
+  size_t row_off = static_cast<size_t>(row0) * p.K;
 #pragma unroll
   for (int u = 0; u < kPullUnroll; ++u) {
     const int vidx = u * 32 + lane;
-    if (vidx < k.nvec) {
-      const int rr = vidx / vec_per_row;
-      const int cc = vidx - rr * vec_per_row;
-      *reinterpret_cast<uint4*>(k.dst + static_cast<size_t>(rr) * p.K + cc * 8) = regs[u];
+    if (vidx < k.nvec) *reinterpret_cast<uint4*>(k.dst + row_off + cc * 8) = regs[u];
+    cc += 32;
+    if (cc >= vec_per_row) {
+      cc -= vec_per_row;
+      row_off += p.K;
+      if (cc >= vec_per_row) {
+        cc -= vec_per_row;
+        row_off += p.K;
+      }
     }
   }
 }
@@ -291,28 +323,28 @@ struct WorkItem {
   int part_cols[2];
 };
 
-__device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int item) {
-  int m_idx, n0_units, w_units;
-  if (p.items != nullptr) {
-    const uint32_t e = __ldg(p.items + item);
-    if (e == kNoItem) {
-      WorkItem none;
-      none.m_idx = none.n0 = none.parts = 0;
-      none.part_cols[0] = none.part_cols[1] = 0;
-      return none;
-    }
-    m_idx = static_cast<int>(e & 0x3FFFu);
-    n0_units = static_cast<int>((e >> 14) & 0xFFFu);
-    w_units = static_cast<int>((e >> 26) & 0x7u) + 1;
-  } else {
-    m_idx = item / p.row_len;
-    const int pos = item - m_idx * p.row_len;
-    n0_units = pos * p.row_base + (pos < p.row_extra ? pos : p.row_extra);
-    w_units = p.row_base + (pos < p.row_extra ? 1 : 0);
-  }
+// The list entry of work item `item` (kNoItem past the end). Every role fetches
+// the entry of its next item while it works on the current one, and the first
+// entry before the kernel's set-up, so the fetch never sits between two items.
+__device__ __forceinline__ uint32_t item_entry(const GemmParams& p, int item) {
+  if (item >= p.num_items) return kNoItem;
+  if (p.items != nullptr) return __ldg(p.items + item);
+  const int m_idx = item / p.row_len;
+  const int pos = item - m_idx * p.row_len;
+  return encode_item(m_idx, pos * p.row_base + (pos < p.row_extra ? pos : p.row_extra),
+                     p.row_base + (pos < p.row_extra ? 1 : 0));
+}
+
+__device__ __forceinline__ WorkItem decode_entry(uint32_t e) {
   WorkItem w;
-  w.m_idx = m_idx;
-  w.n0 = n0_units * kUnit;
+  if (e == kNoItem) {
+    w.m_idx = w.n0 = w.parts = 0;
+    w.part_cols[0] = w.part_cols[1] = 0;
+    return w;
+  }
+  const int w_units = static_cast<int>((e >> 26) & 0x7u) + 1;
+  w.m_idx = static_cast<int>(e & 0x3FFFu);
+  w.n0 = static_cast<int>((e >> 14) & 0xFFFu) * kUnit;
   if (w_units * kUnit <= kBlockN) {
     w.parts = 1;
     w.part_cols[0] = w_units * kUnit;
@@ -337,8 +369,6 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   const int cluster_id = blockIdx.x / G;
   const int num_clusters = gridDim.x / G;
   const int num_items = p.num_items;
-  const int num_stages = tile_stages(p.max_item_cols, G);
-  const uint32_t stage_bytes = static_cast<uint32_t>(tile_stage_bytes(p.max_item_cols, G));
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_base = smem_base + Cfg::kOffBar;
@@ -355,6 +385,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     trace[kTraceStart] = clock64();
     trace[kTraceNsStart] = globaltimer_ns();
   }
+  const uint32_t first_entry = item_entry(p, cluster_id);  // the list is written when the plan is made
   // Pull mode: every pull warp claims its pre-assigned first chunk for this
   // launch. The claim words only ever grow (launch ordinals), so the claim may
   // be made before the previous launch of the plan has completed, and its
@@ -371,7 +402,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   if (threadIdx.x == 0) {
     *abort_flag = 0u;
     if ((smem_base & 1023u) != 0u) report_status(p, abort_flag, ST_SMEM_MISALIGNED, smem_base);
-    for (int s = 0; s < num_stages; ++s) {
+    for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -408,26 +439,47 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   // ------------------------------------------------------------ TMA producer
   if (warp == 0 && !misaligned) {
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
-      uint32_t in_flight = 0;  // loads armed so far (saturates at the stage count)
+      uint32_t stage = 0;
+      uint32_t fills = 0;      // bit s: parity of the number of times stage s has been armed
+      uint32_t in_flight = 0;  // stages armed so far in the current ring (saturates at its length)
+      int num_stages = 0;      // current ring: length and stage size (0: nothing loaded yet)
+      uint32_t stage_bytes = 0;
       bool ok = true;
       long long waited = 0;
       const uint32_t leader_full0 = (G == 2) ? mapa_cluster(full_bar(0), 0) : full_bar(0);
       const bool hints = (p.flags & kFlagNoL2Hints) == 0u;
       const uint64_t keep = l2_policy_evict_last();  // W is re-read by every round of items
-      auto advance = [&](uint32_t& s, uint32_t& ph) {
-        if (++s == static_cast<uint32_t>(num_stages)) {
-          s = 0;
-          ph ^= 1u;
-        }
+      // A stage may be armed again once the MMAs of its previous use have read it:
+      // the empty barrier's phase of that use has the parity of (uses - 1).
+      auto empty_parity = [&](uint32_t s) { return ((fills >> s) & 1u) ^ 1u; };
+      auto advance = [&](uint32_t& s) {
+        if (++s == static_cast<uint32_t>(num_stages)) s = 0;
       };
+      uint32_t entry = first_entry;
       for (int item = cluster_id; item < num_items && ok; item += num_clusters) {
-        const WorkItem w = decode_item(p, item);
+        const WorkItem w = decode_entry(entry);
+        entry = item_entry(p, item + num_clusters);
         if (w.parts == 0) continue;
         const int panel = w.m_idx * G + static_cast<int>(cta_rank);
         const int a_row0 = panel * kBlockM;
         const int item_cols = w.part_cols[0] + w.part_cols[1];
         const uint32_t item_bytes = static_cast<uint32_t>(tile_stage_bytes(item_cols, G));
+        const uint32_t class_bytes = static_cast<uint32_t>(tile_stage_bytes(stage_class_cols(item_cols), G));
+        if (class_bytes != stage_bytes) {
+          // Another stage geometry: wait until every stage of the old ring has been
+          // consumed (the new stages overlap them), then start over at stage 0.
+          for (int s = 0; s < num_stages && ok; ++s) {
+            if (!mbar_wait_bounded(empty_bar(s), empty_parity(s), abort_flag, timeout_ns)) {
+              report_status(p, abort_flag, ST_PRODUCER_SLOT_TIMEOUT, static_cast<uint32_t>(item));
+              ok = false;
+            }
+          }
+          if (!ok) break;
+          stage_bytes = class_bytes;
+          num_stages = tile_stages(stage_class_cols(item_cols), G);
+          stage = 0;
+          in_flight = 0;
+        }
         // Arm a stage for the bytes of one K step of this item (for a CTA pair
         // both CTAs' loads complete on the leader's barrier, armed for both).
         auto arm = [&](uint32_t s) {
@@ -436,6 +488,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           } else {
             if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * item_bytes);
           }
+          fills ^= 1u << s;
         };
         auto load_a = [&](uint32_t s, int kt) {
           const uint32_t dst = smem_base + s * stage_bytes;
@@ -483,11 +536,11 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
             // the A boxes remain to be fetched once the gate opens.
             int pre = 0;
             if ((p.flags & kFlagNoWPrefetch) == 0u) {
-              uint32_t s = stage, ph = phase;
-              while (pre < num_stages && pre < p.k_tiles && mbar_test_wait(empty_bar(s), ph ^ 1u)) {
+              uint32_t s = stage;
+              while (pre < num_stages && pre < p.k_tiles && mbar_test_wait(empty_bar(s), empty_parity(s))) {
                 arm(s);
                 load_w(s, pre);
-                advance(s, ph);
+                advance(s);
                 ++pre;
               }
             }
@@ -512,7 +565,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
             for (int j = 0; j < pre; ++j) {
               load_a(stage, j);
               if (in_flight < static_cast<uint32_t>(num_stages)) ++in_flight;
-              advance(stage, phase);
+              advance(stage);
             }
             kt_begin = pre;
             if (!ok) break;
@@ -523,7 +576,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
         for (int kt = kt_begin; kt < p.k_tiles; ++kt) {
           const long long t_wait = trace ? clock64() : 0;
-          const bool free_stage = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, timeout_ns);
+          const bool free_stage = mbar_wait_bounded(empty_bar(stage), empty_parity(stage), abort_flag, timeout_ns);
           if (trace) waited += clock64() - t_wait;
           if (!free_stage) {
             report_status(p, abort_flag, ST_PRODUCER_SLOT_TIMEOUT, static_cast<uint32_t>(item));
@@ -535,28 +588,26 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           load_a(stage, kt);
           load_w(stage, kt);
           if (in_flight < static_cast<uint32_t>(num_stages)) ++in_flight;
-          advance(stage, phase);
+          advance(stage);
         }
       }
       if (trace) trace[kTraceProdWait] = static_cast<unsigned long long>(waited);
       if (!ok) {
         // Giving up: let loads that are still in flight land before the CTA
         // retires. A lone CTA (and the leader of a pair) watches its own full
-        // barriers; the other CTA of a pair has no barrier of its own to watch
-        // and allows the same 2 ms per stage.
-        uint32_t s = stage, ph = phase;
+        // barriers (the phase of a stage's latest arming has the parity of
+        // uses - 1); the other CTA of a pair has no barrier of its own to watch
+        // and allows the same time.
+        uint32_t s = stage;
         for (uint32_t i = 0; i < in_flight; ++i) {
-          if (s == 0) {
-            s = static_cast<uint32_t>(num_stages);
-            ph ^= 1u;
-          }
+          if (s == 0) s = static_cast<uint32_t>(num_stages);
           --s;
           const uint64_t t0 = globaltimer_ns();
           if (G == 1 || cta_rank == 0) {
-            while (!mbar_try_wait(full_bar(s), ph) && globaltimer_ns() - t0 < 2000000ull) {
+            while (!mbar_try_wait(full_bar(s), ((fills >> s) & 1u) ^ 1u) && globaltimer_ns() - t0 < 2000000ull) {
             }
           } else {
-            while (globaltimer_ns() - t0 < 2000000ull / static_cast<uint64_t>(num_stages)) {
+            while (globaltimer_ns() - t0 < 2000000ull / static_cast<uint64_t>(num_stages > 0 ? num_stages : 1)) {
             }
           }
         }
@@ -577,7 +628,6 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   // accumulator as soon as that part's MMAs are issued.
   if (warp == 1 && !misaligned && cta_rank == 0) {
     const uint64_t desc0 = make_kmajor_sw128_desc(smem_base);
-    const uint64_t desc_step = static_cast<uint64_t>(stage_bytes >> 4);
     const bool pair_commit = (G == 2) && (p.flags & kFlagSplitCommit) == 0u;
     // The fused step needs, for a CTA pair, the commit that reaches both CTAs' barriers at once.
     const bool fused_ok = (G == 1 || pair_commit) && (p.flags & kFlagSeparateIssue) == 0u;
@@ -593,16 +643,34 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
       }
     };
-    uint32_t stage = 0, phase = 0;
+    uint32_t stage = 0;
+    uint32_t uses = 0;        // bit s: parity of the number of times stage s has been consumed
+    int num_stages = 0;       // current ring (see the producer): length and stage size
+    uint32_t stage_bytes = 0;
     uint32_t acc_it = 0;  // parts issued so far: part i uses accumulator slot i & 1
     bool failed = false;
     bool stage_ready = false;  // the probe of the previous step found this stage full
     bool first_mma = true;
     long long wait_full = 0, wait_acc = 0;
     int items_run = 0;
+    uint32_t entry = first_entry;
     for (int item = cluster_id; item < num_items; item += num_clusters, ++items_run) {
-      const WorkItem w = decode_item(p, item);
+      const WorkItem w = decode_entry(entry);
+      entry = item_entry(p, item + num_clusters);
       if (w.parts == 0) continue;
+      {
+        const int class_cols = stage_class_cols(w.part_cols[0] + w.part_cols[1]);
+        const uint32_t class_bytes = static_cast<uint32_t>(tile_stage_bytes(class_cols, G));
+        if (class_bytes != stage_bytes) {
+          // another stage geometry: everything issued so far has been consumed here,
+          // the producer restarts at stage 0 as well
+          stage_bytes = class_bytes;
+          num_stages = tile_stages(class_cols, G);
+          stage = 0;
+          stage_ready = false;
+        }
+      }
+      const uint64_t desc_step = static_cast<uint64_t>(stage_bytes >> 4);
       uint32_t slot[2], d_tmem[2], idesc[2];
       uint64_t b_off[2];
       uint32_t b_bytes = 0;
@@ -616,7 +684,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       for (int kt = 0; kt < p.k_tiles; ++kt) {
         if (!stage_ready) {
           const long long t_full = trace ? clock64() : 0;
-          if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, timeout_ns)) {
+          if (!mbar_wait_bounded(full_bar(stage), (uses >> stage) & 1u, abort_flag, timeout_ns)) {
             report_status(p, abort_flag, ST_MMA_FULL_TIMEOUT, static_cast<uint32_t>(item));
             failed = true;
           }
@@ -626,11 +694,10 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (trace && first_mma && lane == 0) trace[kTraceFirstMmaNs] = globaltimer_ns() - trace[kTraceNsStart];
         first_mma = false;
         const uint64_t a_desc = desc0 + desc_step * stage;
-        uint32_t next_stage = stage + 1u, next_phase = phase;
-        if (next_stage == static_cast<uint32_t>(num_stages)) {
-          next_stage = 0;
-          next_phase ^= 1u;
-        }
+        uses ^= 1u << stage;
+        uint32_t next_stage = stage + 1u;
+        if (next_stage == static_cast<uint32_t>(num_stages)) next_stage = 0;
+        const uint32_t next_phase = (uses >> next_stage) & 1u;
         const bool edge = (kt == 0) || (kt == p.k_tiles - 1);
         if (fused_ok && !edge) {
           // The MMAs of the stage, the commit that frees it and a probe of the
@@ -676,7 +743,6 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           stage_ready = false;
         }
         stage = next_stage;
-        phase = next_phase;
       }
       acc_it += static_cast<uint32_t>(w.parts);
       // A lane whose wait ran out has raised the abort flag, which makes every
@@ -702,14 +768,22 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     bool ok = true;
     long long epi_wait = 0;
     bool handoff_checked = false;
+    uint32_t entry = first_entry;
     for (int item = cluster_id; item < num_items && ok; item += num_clusters) {
-      const WorkItem w = decode_item(p, item);
+      const WorkItem w = decode_entry(entry);
+      entry = item_entry(p, item + num_clusters);
       if (w.parts == 0) continue;
       const int row0 = (w.m_idx * G + static_cast<int>(cta_rank)) * kBlockM + q * kEpiRows;
       int part_col0 = w.n0;
       for (int part = 0; part < w.parts && ok; ++part, ++acc_it) {
         const uint32_t as = acc_it & 1u;
         const uint32_t aphase = (acc_it >> 1) & 1u;
+        // The bias of a 64-column sub-tile is fetched one sub-tile ahead (here: before the
+        // wait for the accumulator), so that its global-memory latency never sits
+        // between two reads of TMEM: the slot is handed back after the last read.
+        uint32_t bias_next = 0u;
+        if (p.bias != nullptr && part_col0 < p.N)
+          bias_next = *reinterpret_cast<const uint32_t*>(p.bias + part_col0 + 2 * lane);
 
         const long long t_epi = trace ? clock64() : 0;
         const bool got = mbar_wait_bounded(acc_full_bar(as), aphase, abort_flag, timeout_ns);
@@ -726,11 +800,12 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           const int gcol = part_col0 + c * kEpiCols;
           const bool in_range = gcol < p.N;
           // Bias for these 64 columns, widened to FP32, shared inside the warp.
-          if (p.bias != nullptr && in_range) {
-            const __nv_bfloat162 b2 =
-                *reinterpret_cast<const __nv_bfloat162*>(p.bias + gcol + 2 * lane);
+          if (p.bias != nullptr) {
+            const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&bias_next);
             bias_s[2 * lane] = __bfloat162float(b2.x);
             bias_s[2 * lane + 1] = __bfloat162float(b2.y);
+            if (c + 1 < chunks && gcol + kEpiCols < p.N)
+              bias_next = *reinterpret_cast<const uint32_t*>(p.bias + gcol + kEpiCols + 2 * lane);
           }
           uint32_t v[2][32];
           const uint32_t taddr =
@@ -864,6 +939,8 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       int pending_panel = -1;
       int tickets_done = 0;
+      const int lane_row0 = lane / (p.shard >> 3);  // lane's first vector inside a ticket
+      const int lane_vec0 = lane - lane_row0 * (p.shard >> 3);
       // The first chunk of every pull warp is its own index (no cursor draw on the
       // critical path of the first panels); the cursor hands out the rest. Once
       // the cursor has run out, a warp looks for first chunks whose owner has
@@ -886,12 +963,12 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           for (int i = 0; i < kPullChunk; ++i) {
             const unsigned long long t = t_first + static_cast<unsigned long long>(i) * stride;
             if (t >= total) break;
-            const PullTicket k = pull_ticket_geometry(p, t);
+            const PullTicket k = pull_ticket_geometry(p, static_cast<uint32_t>(t));
             const int panel = k.panel;
             uint4 regs[kPullUnroll];
-            pull_ticket_load(p, k, lane, regs);
+            pull_ticket_load(k, lane, regs);
             if (pending_panel >= 0) publish(pending_panel);
-            pull_ticket_store(p, k, lane, regs);
+            pull_ticket_store(p, k, lane, lane_row0, lane_vec0, regs);
             __syncwarp();
             pending_panel = panel;
             if (tickets_done < 2) {

@@ -1,0 +1,141 @@
+"""Where the time of one fused operation goes on real peers: CUDA events between the
+launches of a peer-write call (GEMM with routed stores | copy-out of the slots)
+and of a pull call (staging copy | pull + GEMM), on the Wan2.1-14B-shaped
+projection, next to the kernels timed alone and the whole call.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node U --master-addr 127.0.0.1 \
+        --master-port 29545 -m megaup_b200.handoff_profile [--iters 30]
+
+Run it once per hand-off protocol (``MEGA_UP_FUSED_SYNC=1``, the default: the
+hand-offs ride inside the kernels; ``=0``: two stand-alone barrier kernels per
+operation, which then show up inside the second segment of each call). An
+event between two launches takes away their programmatic overlap, so the
+segments add up to a little more than the call timed as a whole; the
+difference is printed. Every figure is the maximum over the ranks of the
+rank's median. Rank 0 prints one ``[HANDOFF_PROFILE] {json}`` line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+import torch.distributed as dist
+
+import megaup_b200 as mega_up
+from megaup_b200 import runtime as runtime_module
+
+HIDDEN, HEADS, HEAD_DIM, TOKENS = 5120, 40, 128, 4096
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--iters", type=int, default=30)
+    args = parser.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=device)
+    up = world
+    runtime = mega_up.initialize_runtime(dist.group.WORLD, hidden=HIDDEN, max_rows=TOKENS, device=device)
+    gen = torch.Generator(device=device).manual_seed(99 + rank)
+
+    def randn(shape, scale=1.0):
+        return (torch.randn(shape, device=device, generator=gen) * scale).to(torch.bfloat16)
+
+    w, b = randn((HIDDEN, HIDDEN), HIDDEN ** -0.5), randn((HIDDEN,), 0.02)
+    x = randn((1, TOKENS, HEADS, HEAD_DIM))
+    hx = randn((1, up * TOKENS, HEADS // up, HEAD_DIM))
+    out = torch.empty((1, up * TOKENS, HEADS // up, HEAD_DIM), dtype=torch.bfloat16, device=device)
+    kw = dict(batch=1, sequence=TOKENS, heads=HEADS, head_dim=HEAD_DIM, bias=b)
+    writer = mega_up.prepare_peer_write_gemm_bshd(w, runtime, **kw)
+    puller = mega_up.prepare_headshard_pull_gemm_bshd(w, runtime, **kw)
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+
+    def sync_all() -> None:
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def reduce_max(values: list[float]) -> list[float]:
+        t = torch.tensor(values, dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    def median_us(samples: list[list[float]]) -> list[float]:
+        return reduce_max([statistics.median(column) for column in zip(*samples)])
+
+    def whole(call) -> float:
+        for _ in range(3):
+            call()
+        sync_all()
+        events[0].record()
+        for _ in range(args.iters):
+            call()
+        events[1].record()
+        sync_all()
+        return reduce_max([events[0].elapsed_time(events[1]) * 1e3 / args.iters])[0]
+
+    def segments(first, second) -> list[float]:
+        """[first launch, second launch] of one operation, an event in between; the
+        calls are enqueued back to back (as in the whole-call timing) and the
+        events read afterwards."""
+
+        total = args.iters + 3
+        marks = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(total)]
+        sync_all()
+        for it in range(total):
+            with torch.no_grad(), runtime.lease():
+                marks[it][0].record()
+                first()
+                marks[it][1].record()
+                second()
+                marks[it][2].record()
+        sync_all()
+        samples = [
+            [m[0].elapsed_time(m[1]) * 1e3, m[1].elapsed_time(m[2]) * 1e3] for m in marks[3:]
+        ]
+        return median_us(samples)
+
+    x2d = x.view(TOKENS, HIDDEN)
+    report: dict[str, object] = {
+        "up": up,
+        "handoff": "folded into the kernels" if runtime_module._FUSED_SYNC else "two barrier kernels per operation",
+    }
+    report["peer_write_call_us"] = whole(lambda: writer(x, out=out, validate_group=False))
+    report["pull_call_us"] = whole(lambda: puller(hx, validate_group=False))
+    report["peer_write_kernel_alone_us"] = whole(lambda: writer.launch(x2d))
+
+    def pull_alone() -> None:
+        if puller.compiled.epoch >= puller.compiled.workspace_epochs:
+            puller.compiled.reset_workspace()
+        puller.compiled()
+
+    report["pull_kernel_alone_us"] = whole(pull_alone)
+    sync_all()
+    gemm_us, copy_out_us = segments(lambda: writer._launch(x), lambda: writer._materialize(out))
+    stage_us, pull_us = segments(lambda: (puller._refresh_workspace(), puller._stage(hx)), puller._launch)
+    report["peer_write_segments_us"] = {"gemm_with_routed_stores": gemm_us, "copy_out_with_its_waits": copy_out_us}
+    report["pull_segments_us"] = {"staging_copy_with_its_waits": stage_us, "pull_gemm_with_its_waits": pull_us}
+    report["event_overhead_us"] = {
+        "peer_write": gemm_us + copy_out_us - report["peer_write_call_us"],
+        "pull": stage_us + pull_us - report["pull_call_us"],
+    }
+    report["call_minus_kernel_us"] = {
+        "peer_write": report["peer_write_call_us"] - report["peer_write_kernel_alone_us"],
+        "pull": report["pull_call_us"] - report["pull_kernel_alone_us"],
+    }
+    torch.cuda.synchronize(device)
+    runtime.check_status()
+    if rank == 0:
+        print("[HANDOFF_PROFILE] " + json.dumps(report), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -103,7 +103,9 @@ class CompiledHeadShardPullGemm:
         self.cta_group = group.value
         self.smem_bytes = smem.value
         # descriptors the reference's compiled object carries (run_pull_gemm_contention.py:225-254)
-        stage_bytes = 128 * 64 * 2 + (self.tile_n // self.cta_group) * 64 * 2
+        # stage geometry of the widest work item (classes of 128, 256 and 512 columns)
+        class_cols = 128 if self.tile_n <= 128 else 256 if self.tile_n <= 256 else 512
+        stage_bytes = 128 * 64 * 2 + (class_cols // self.cta_group) * 64 * 2
         self.num_ab_stages = min(8, 196608 // stage_bytes)
         self.num_c_stages = 2
         self.enable_bulk_pull = False

@@ -154,10 +154,18 @@ def main() -> int:
             "mma_wait_accumulator_mean": float(leaders[:, 3].mean()),
             "producer_wait_stage_mean": float(t[:, 4].mean()),
             "epilogue_wait_mean": float(t[:, 5].mean()),
+            "setup_done_us_mean_max": [float(t[:, 12].mean()) / 1e3, float(t[:, 12].max()) / 1e3],
+            "first_operands_us_min_mean_max": [
+                float(leaders[:, 14].min()) / 1e3, float(leaders[:, 14].mean()) / 1e3, float(leaders[:, 14].max()) / 1e3,
+            ],
+            "items_per_cta_min_max": [float(leaders[:, 15].min()), float(leaders[:, 15].max())],
         }
         if args.mode == "pull":
             report["trace"]["pull_done_us_after_start"] = float(t[:, 8].max() - t[:, 6].min()) / 1e3
             report["trace"]["pull_tickets_min_max"] = [float(t[:, 9].min()), float(t[:, 9].max())]
+            report["trace"]["first_ticket_stored_us_min_mean_max"] = [
+                float(t[:, 13].min()) / 1e3, float(t[:, 13].mean()) / 1e3, float(t[:, 13].max()) / 1e3,
+            ]
             gate = t[:, 10] / 1e3
             report["trace"]["first_gate_open_us_min_mean_max"] = [float(gate.min()), float(gate.mean()), float(gate.max())]
             report["trace"]["gate_cycles_mean"] = float(t[:, 11].mean())

@@ -20,10 +20,13 @@ def _group_size() -> int:
     return 8 if count >= 8 else 4 if count >= 4 else 2 if count >= 2 else 0
 
 
-@pytest.mark.parametrize("handoff", ["barrier_kernels", "folded_into_kernels"])
+@pytest.mark.parametrize("handoff", ["folded_into_kernels", "barrier_kernels"])
 def test_fused_operators_match_cublas_plus_nccl(handoff: str) -> None:
-    """Both slot hand-off protocols: two stand-alone barrier kernels per operation (the
-    default) and the hand-off folded into the producing / consuming kernels."""
+    """Both slot hand-off protocols: the hand-off folded into the producing / consuming
+    kernels (the default) and two stand-alone barrier kernels per operation. The run
+    covers every layout, the reference's multi-GPU shape matrix for this group size,
+    the collective rejections, a hand-off that times out, and (--full) the
+    Wan2.1-14B, Llama-3-8B, Llama-3-70B and edge-shape configurations on real peers."""
 
     import os
 
@@ -34,8 +37,9 @@ def test_fused_operators_match_cublas_plus_nccl(handoff: str) -> None:
     command = [
         sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={up}",
         "--master-addr", "127.0.0.1", "--master-port", "29533", str(ROOT / "tests" / "run_distributed.py"),
+        "--full", "--stress", "20",
     ]
-    result = subprocess.run(command, capture_output=True, text=True, timeout=900, cwd=ROOT, env=env)
+    result = subprocess.run(command, capture_output=True, text=True, timeout=1500, cwd=ROOT, env=env)
     lines = [line for line in result.stdout.splitlines() if line.startswith("[CORRECTNESS_RESULT]")]
     assert result.returncode == 0 and lines, result.stdout[-4000:] + result.stderr[-4000:]
     report = json.loads(lines[-1].split(" ", 1)[1])
