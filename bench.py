@@ -642,7 +642,14 @@ def main() -> None:
                 "ms_per_step": soak_ms_per_step,
                 "steps": soak,
             },
-            "gpu_launches": args.steps * (4 if not distributed else 8),
+            # per step: GEMM + copy-out, staging copy + GEMM, plus the barrier kernels of the hand-off protocol
+            "gpu_launches": args.steps * {"none": 4, "folded": 4, "lazy": 6, "barriers": 8}[runtime.handoff],
+            "handoff": {
+                "none": "emulated peers on one stream",
+                "lazy": "one barrier kernel per operation, second hand-off signalled from the last kernel's tail",
+                "folded": "both hand-offs folded into the kernels",
+                "barriers": "two barrier kernels per operation",
+            }[runtime.handoff],
             "kernels": {
                 "cta_group": peer_write.launch.cta_group,
                 "grid_ctas": peer_write.launch.grid_ctas,

@@ -554,7 +554,11 @@ Schedule choose_schedule(int mode, int m_tiles, int n, int k_tiles, int up, int 
   o.up = up;
   o.rank = rank;
   o.rotate = (mode == mup::MODE_PEER_WRITE);
-  o.band = o.rotate ? std::max(1, env_int("MEGA_UP_BAND", 1)) : 1;
+  // Peer-write lists walk bands of 16 M tiles column by column (148.9 against
+  // 150.7 us for 4096 x 5120 x 5120: the CTA pairs of a round then share W boxes
+  // rather than A boxes); pull lists stay row by row, the order in which the
+  // pulled rows arrive.
+  o.band = o.rotate ? std::max(1, env_int("MEGA_UP_BAND", 16)) : 1;
   o.slots = slots;
   o.k_tiles = k_tiles;
   o.g = g;

@@ -129,8 +129,8 @@ __host__ __device__ constexpr int tile_stages(int cols, int g) {
 // the TMA producer lets the pipeline drain (every stage consumed) and both
 // sides restart at stage 0; which phase of a stage's barriers comes next is
 // kept per stage, one bit each, so the ring may change its length.
-__host__ __device__ constexpr int stage_class_cols(int cols) {
-  return cols <= 2 * kUnit ? 2 * kUnit : (cols <= kBlockN ? kBlockN : kMaxItemUnits * kUnit);
+__host__ __device__ constexpr int stage_class_cols(int cols, bool narrow_class = true) {
+  return (narrow_class && cols <= 2 * kUnit) ? 2 * kUnit : (cols <= kBlockN ? kBlockN : kMaxItemUnits * kUnit);
 }
 
 // A work item as the host lists it: 14 bits M tile, 12 bits first column / 64, 3 bits (columns / 64 - 1).
@@ -204,6 +204,9 @@ constexpr unsigned int kFlagNoL2Hints = 8u;     // tuning: drop the L2 hints (W 
 constexpr unsigned int kFlagSplitCommit = 1u;  // G=2: one commit per CTA of the pair instead of one for both
 constexpr unsigned int kFlagSeparateIssue = 2u;  // tuning: poll, MMAs and commit as separate statements (the slower issue loop)
 constexpr unsigned int kFlagPullExtraFence = 16u;  // tuning: an explicit fence.acq_rel.gpu before every release of a ready count
+constexpr unsigned int kFlagSpinWaits = 256u;  // tuning: the TMA producer and the MMA warp poll their barriers with test_wait
+constexpr unsigned int kFlagNoNarrowClass = 128u;  // tuning: items of at most 128 columns use the 256-column stage geometry
+constexpr unsigned int kFlagNoPartSkew = 64u;   // tuning: two-accumulator items without the skew between their parts
 constexpr unsigned int kFlagNoWPrefetch = 32u;  // tuning: pull mode, do not load W ahead of a closed panel gate
 
 // The first role of a CTA that gives up records why; roles that give up because
@@ -464,7 +467,9 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         const int a_row0 = panel * kBlockM;
         const int item_cols = w.part_cols[0] + w.part_cols[1];
         const uint32_t item_bytes = static_cast<uint32_t>(tile_stage_bytes(item_cols, G));
-        const uint32_t class_bytes = static_cast<uint32_t>(tile_stage_bytes(stage_class_cols(item_cols), G));
+        const bool narrow_class = (p.flags & kFlagNoNarrowClass) == 0u;
+        const uint32_t class_bytes =
+            static_cast<uint32_t>(tile_stage_bytes(stage_class_cols(item_cols, narrow_class), G));
         if (class_bytes != stage_bytes) {
           // Another stage geometry: wait until every stage of the old ring has been
           // consumed (the new stages overlap them), then start over at stage 0.
@@ -476,7 +481,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
           if (!ok) break;
           stage_bytes = class_bytes;
-          num_stages = tile_stages(stage_class_cols(item_cols), G);
+          num_stages = tile_stages(stage_class_cols(item_cols, narrow_class), G);
           stage = 0;
           in_flight = 0;
         }
@@ -490,35 +495,40 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
           fills ^= 1u << s;
         };
+        // A carries no L2 hint: its rows are read by the items of one M tile and then
+        // dead, while W (evict-last) is read again by every round of items.
         auto load_a = [&](uint32_t s, int kt) {
           const uint32_t dst = smem_base + s * stage_bytes;
           const uint32_t bar = (G == 2) ? leader_full0 + 8u * s : full_bar(s);
           if constexpr (G == 1) {
-            if (hints) tma_load_2d_hint(dst, &p.map_a, kt * kBlockK, a_row0, bar, keep);
-            else tma_load_2d(dst, &p.map_a, kt * kBlockK, a_row0, bar);
+            tma_load_2d(dst, &p.map_a, kt * kBlockK, a_row0, bar);
           } else {
-            if (hints) tma_load_2d_pair_hint(dst, &p.map_a, kt * kBlockK, a_row0, bar, keep);
-            else tma_load_2d_pair(dst, &p.map_a, kt * kBlockK, a_row0, bar);
+            tma_load_2d_pair(dst, &p.map_a, kt * kBlockK, a_row0, bar);
+          }
+        };
+        // W boxes of the item's one or two parts: tensor map, first row and offset inside a stage.
+        const int rows0 = tile_b_rows(w.part_cols[0], G);
+        const CUtensorMap* const map0 = &p.map_b[w.part_cols[0] / kUnit - 1];
+        const int w_row0 = w.n0 + static_cast<int>(cta_rank) * rows0;
+        const bool two_parts = (w.parts == 2);
+        const int rows1 = two_parts ? tile_b_rows(w.part_cols[1], G) : 0;
+        const CUtensorMap* const map1 = &p.map_b[two_parts ? w.part_cols[1] / kUnit - 1 : 0];
+        const int w_row1 = w.n0 + w.part_cols[0] + static_cast<int>(cta_rank) * rows1;
+        const uint32_t w_off1 = Cfg::kABytes + static_cast<uint32_t>(rows0) * kBlockK * 2;
+        auto load_box = [&](uint32_t dst, const CUtensorMap* map, int kt, int row0, uint32_t bar) {
+          if constexpr (G == 1) {
+            if (hints) tma_load_2d_hint(dst, map, kt * kBlockK, row0, bar, keep);
+            else tma_load_2d(dst, map, kt * kBlockK, row0, bar);
+          } else {
+            if (hints) tma_load_2d_pair_hint(dst, map, kt * kBlockK, row0, bar, keep);
+            else tma_load_2d_pair(dst, map, kt * kBlockK, row0, bar);
           }
         };
         auto load_w = [&](uint32_t s, int kt) {
-          uint32_t dst = smem_base + s * stage_bytes + Cfg::kABytes;
+          const uint32_t base = smem_base + s * stage_bytes;
           const uint32_t bar = (G == 2) ? leader_full0 + 8u * s : full_bar(s);
-          int col0 = w.n0;
-          for (int part = 0; part < w.parts; ++part) {
-            const int rows = tile_b_rows(w.part_cols[part], G);
-            const CUtensorMap* map = &p.map_b[w.part_cols[part] / kUnit - 1];
-            const int row0 = col0 + static_cast<int>(cta_rank) * rows;
-            if constexpr (G == 1) {
-              if (hints) tma_load_2d_hint(dst, map, kt * kBlockK, row0, bar, keep);
-              else tma_load_2d(dst, map, kt * kBlockK, row0, bar);
-            } else {
-              if (hints) tma_load_2d_pair_hint(dst, map, kt * kBlockK, row0, bar, keep);
-              else tma_load_2d_pair(dst, map, kt * kBlockK, row0, bar);
-            }
-            dst += static_cast<uint32_t>(rows) * kBlockK * 2;
-            col0 += w.part_cols[part];
-          }
+          load_box(base + Cfg::kABytes, map0, kt, w_row0, bar);
+          if (two_parts) load_box(base + w_off1, map1, kt, w_row1, bar);
         };
         int kt_begin = 0;
         if constexpr (MODE == MODE_PULL) {
@@ -576,7 +586,8 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
         for (int kt = kt_begin; kt < p.k_tiles; ++kt) {
           const long long t_wait = trace ? clock64() : 0;
-          const bool free_stage = mbar_wait_bounded(empty_bar(stage), empty_parity(stage), abort_flag, timeout_ns);
+          const bool free_stage = mbar_wait_bounded(empty_bar(stage), empty_parity(stage), abort_flag, timeout_ns,
+                                                    (p.flags & kFlagSpinWaits) != 0u);
           if (trace) waited += clock64() - t_wait;
           if (!free_stage) {
             report_status(p, abort_flag, ST_PRODUCER_SLOT_TIMEOUT, static_cast<uint32_t>(item));
@@ -659,7 +670,8 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       entry = item_entry(p, item + num_clusters);
       if (w.parts == 0) continue;
       {
-        const int class_cols = stage_class_cols(w.part_cols[0] + w.part_cols[1]);
+        const int class_cols =
+            stage_class_cols(w.part_cols[0] + w.part_cols[1], (p.flags & kFlagNoNarrowClass) == 0u);
         const uint32_t class_bytes = static_cast<uint32_t>(tile_stage_bytes(class_cols, G));
         if (class_bytes != stage_bytes) {
           // another stage geometry: everything issued so far has been consumed here,
@@ -671,78 +683,185 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
       }
       const uint64_t desc_step = static_cast<uint64_t>(stage_bytes >> 4);
-      uint32_t slot[2], d_tmem[2], idesc[2];
-      uint64_t b_off[2];
-      uint32_t b_bytes = 0;
-      for (int part = 0; part < 2; ++part) {
-        slot[part] = (acc_it + part) & 1u;
-        d_tmem[part] = tmem_base + slot[part] * kBlockN;
-        idesc[part] = make_idesc_bf16(Cfg::kUmmaM, w.part_cols[part] > 0 ? w.part_cols[part] : kUnit);
-        b_off[part] = static_cast<uint64_t>((Cfg::kABytes + b_bytes) >> 4);
-        b_bytes += static_cast<uint32_t>(tile_b_rows(w.part_cols[part], G)) * kBlockK * 2;
-      }
-      for (int kt = 0; kt < p.k_tiles; ++kt) {
+      const uint32_t slot0 = acc_it & 1u, slot1 = slot0 ^ 1u;
+      const uint32_t d_tmem0 = tmem_base + slot0 * kBlockN, d_tmem1 = tmem_base + slot1 * kBlockN;
+      const uint32_t idesc0 = make_idesc_bf16(Cfg::kUmmaM, w.part_cols[0]);
+      const uint32_t idesc1 = make_idesc_bf16(Cfg::kUmmaM, w.parts == 2 ? w.part_cols[1] : kUnit);
+      const uint64_t b_off0 = static_cast<uint64_t>(Cfg::kABytes >> 4);
+      const uint64_t b_off1 =
+          b_off0 + static_cast<uint64_t>((static_cast<uint32_t>(tile_b_rows(w.part_cols[0], G)) * kBlockK * 2) >> 4);
+      uint64_t a_desc = desc0 + desc_step * stage;
+      // Wait (unless the previous step's probe saw it) until the operands of `stage` have landed.
+      auto wait_operands = [&]() {
         if (!stage_ready) {
           const long long t_full = trace ? clock64() : 0;
-          if (!mbar_wait_bounded(full_bar(stage), (uses >> stage) & 1u, abort_flag, timeout_ns)) {
+          if (!mbar_wait_bounded(full_bar(stage), (uses >> stage) & 1u, abort_flag, timeout_ns,
+                                 (p.flags & kFlagSpinWaits) != 0u)) {
             report_status(p, abort_flag, ST_MMA_FULL_TIMEOUT, static_cast<uint32_t>(item));
             failed = true;
           }
           if (trace) wait_full += clock64() - t_full;
           tc_fence_after_sync();
         }
-        if (trace && first_mma && lane == 0) trace[kTraceFirstMmaNs] = globaltimer_ns() - trace[kTraceNsStart];
-        first_mma = false;
-        const uint64_t a_desc = desc0 + desc_step * stage;
+      };
+      auto next_of = [&](uint32_t s) { return (s + 1u == static_cast<uint32_t>(num_stages)) ? 0u : s + 1u; };
+      // First and last K step: separate statements. The first waits for each
+      // accumulator slot just before the MMAs that overwrite it, the last
+      // publishes each part's accumulator as soon as that part's MMAs are issued.
+      auto edge_step = [&](bool first, bool last) {
+        wait_operands();
         uses ^= 1u << stage;
-        uint32_t next_stage = stage + 1u;
-        if (next_stage == static_cast<uint32_t>(num_stages)) next_stage = 0;
-        const uint32_t next_phase = (uses >> next_stage) & 1u;
-        const bool edge = (kt == 0) || (kt == p.k_tiles - 1);
-        if (fused_ok && !edge) {
-          // The MMAs of the stage, the commit that frees it and a probe of the
-          // next stage's barrier as one instruction sequence of the elected lane.
-          uint32_t probed = 0;
+        for (int part = 0; part < w.parts; ++part) {
+          const uint32_t slot = part == 0 ? slot0 : slot1;
+          if (first) {
+            // This part overwrites its accumulator slot: the epilogue must have read the slot's previous part.
+            const uint32_t aphase = ((acc_it + part) >> 1) & 1u;
+            const long long t_acc = trace ? clock64() : 0;
+            if (!mbar_wait_bounded(acc_empty_bar(slot), aphase ^ 1u, abort_flag, timeout_ns)) {
+              report_status(p, abort_flag, ST_MMA_ACC_TIMEOUT, static_cast<uint32_t>(item));
+              failed = true;
+            }
+            if (trace) wait_acc += clock64() - t_acc;
+            tc_fence_after_sync();
+          }
           if (elect_one_sync()) {
-            if (w.parts == 1) {
-              probed = umma_kstep4_probe_next<G>(d_tmem[0], a_desc, a_desc + b_off[0], idesc[0], 1u,
-                                                 empty_bar(stage), full_bar(next_stage), next_phase);
-            } else {
-              probed = umma_kstep8_probe_next<G>(d_tmem[0], d_tmem[1], a_desc, a_desc + b_off[0], a_desc + b_off[1],
-                                                 idesc[0], idesc[1], empty_bar(stage), full_bar(next_stage),
-                                                 next_phase);
-            }
+            // 16 BF16 = 32 bytes further along K inside the 128-byte swizzle row per MMA.
+            const uint32_t d = part == 0 ? d_tmem0 : d_tmem1;
+            const uint32_t idesc = part == 0 ? idesc0 : idesc1;
+            const uint64_t b_desc = a_desc + (part == 0 ? b_off0 : b_off1);
+            umma_bf16<G>(d, a_desc, b_desc, idesc, first ? 0u : 1u);
+            umma_bf16<G>(d, a_desc + 2, b_desc + 2, idesc, 1u);
+            umma_bf16<G>(d, a_desc + 4, b_desc + 4, idesc, 1u);
+            umma_bf16<G>(d, a_desc + 6, b_desc + 6, idesc, 1u);
+            if (last) commit_to(acc_full_bar(slot));  // publish the finished accumulator to the epilogue warps
           }
-          stage_ready = __any_sync(0xffffffffu, probed != 0u);
-        } else {
-          for (int part = 0; part < w.parts; ++part) {
-            if (kt == 0) {
-              // This part overwrites its accumulator slot: the epilogue must have read the slot's previous part.
-              const uint32_t aphase = ((acc_it + part) >> 1) & 1u;
-              const long long t_acc = trace ? clock64() : 0;
-              if (!mbar_wait_bounded(acc_empty_bar(slot[part]), aphase ^ 1u, abort_flag, timeout_ns)) {
-                report_status(p, abort_flag, ST_MMA_ACC_TIMEOUT, static_cast<uint32_t>(item));
-                failed = true;
-              }
-              if (trace) wait_acc += clock64() - t_acc;
-              tc_fence_after_sync();
-            }
-            if (elect_one_sync()) {
-              // 16 BF16 = 32 bytes further along K inside the 128-byte swizzle row per MMA.
-              const uint64_t b_desc = a_desc + b_off[part];
-              umma_bf16<G>(d_tmem[part], a_desc, b_desc, idesc[part], kt > 0 ? 1u : 0u);
-              umma_bf16<G>(d_tmem[part], a_desc + 2, b_desc + 2, idesc[part], 1u);
-              umma_bf16<G>(d_tmem[part], a_desc + 4, b_desc + 4, idesc[part], 1u);
-              umma_bf16<G>(d_tmem[part], a_desc + 6, b_desc + 6, idesc[part], 1u);
-              // Publish the finished accumulator to the epilogue warps.
-              if (kt == p.k_tiles - 1) commit_to(acc_full_bar(slot[part]));
-            }
-          }
-          // Release the shared-memory stage once these MMAs have read it.
-          if (elect_one_sync()) commit_to(empty_bar(stage));
-          stage_ready = false;
         }
-        stage = next_stage;
+        // Release the shared-memory stage once these MMAs have read it.
+        if (elect_one_sync()) commit_to(empty_bar(stage));
+        stage_ready = false;
+        stage = next_of(stage);
+        a_desc = stage == 0u ? desc0 : a_desc + desc_step;
+      };
+      // Four MMAs of one part on the stage whose A descriptor is `a`.
+      auto part_step = [&](int part, uint64_t a, bool overwrite) {
+        if (elect_one_sync()) {
+          const uint32_t d = part == 0 ? d_tmem0 : d_tmem1;
+          const uint32_t idesc = part == 0 ? idesc0 : idesc1;
+          const uint64_t b_desc = a + (part == 0 ? b_off0 : b_off1);
+          umma_bf16<G>(d, a, b_desc, idesc, overwrite ? 0u : 1u);
+          umma_bf16<G>(d, a + 2, b_desc + 2, idesc, 1u);
+          umma_bf16<G>(d, a + 4, b_desc + 4, idesc, 1u);
+          umma_bf16<G>(d, a + 6, b_desc + 6, idesc, 1u);
+        }
+      };
+      auto wait_slot = [&](int part) {
+        const uint32_t slot = part == 0 ? slot0 : slot1;
+        const uint32_t aphase = ((acc_it + part) >> 1) & 1u;
+        const long long t_acc = trace ? clock64() : 0;
+        if (!mbar_wait_bounded(acc_empty_bar(slot), aphase ^ 1u, abort_flag, timeout_ns)) {
+          report_status(p, abort_flag, ST_MMA_ACC_TIMEOUT, static_cast<uint32_t>(item));
+          failed = true;
+        }
+        if (trace) wait_acc += clock64() - t_acc;
+        tc_fence_after_sync();
+      };
+      // An item of two accumulators owns all of TMEM, so its K loop cannot start
+      // before the epilogue has read the previous item. To shorten that wait the
+      // first part runs kSkew K steps ahead of the second at both ends of the
+      // item: at the end its accumulator is complete (and being read out) while
+      // the second part still has kSkew steps to go, and at the start the second
+      // part's slot is only needed kSkew steps after the first's. In between
+      // both parts consume the same stage. The stages of the skewed steps are
+      // released by the second part, the later reader. Each part still sees K
+      // in ascending order.
+      constexpr int kSkew = 2;
+      const int k_last = p.k_tiles - 1;
+      const bool skewed = w.parts == 2 && fused_ok && p.k_tiles >= 2 * kSkew + 2 && num_stages > kSkew &&
+                          (p.flags & kFlagNoPartSkew) == 0u;
+      int kt_from = 1, kt_to = k_last;  // middle steps [kt_from, kt_to)
+      if (skewed) {
+        uint32_t held_stage[kSkew];
+        uint64_t held_desc[kSkew];
+        for (int j = 0; j < kSkew; ++j) {  // first part, steps 0 .. kSkew-1
+          wait_operands();
+          stage_ready = false;
+          if (j == 0) wait_slot(0);
+          part_step(0, a_desc, j == 0);
+          held_stage[j] = stage;
+          held_desc[j] = a_desc;
+          stage = next_of(stage);
+          a_desc = stage == 0u ? desc0 : a_desc + desc_step;
+        }
+        for (int j = 0; j < kSkew; ++j) {  // second part catches up and releases the stages
+          if (j == 0) wait_slot(1);
+          part_step(1, held_desc[j], j == 0);
+          if (elect_one_sync()) commit_to(empty_bar(held_stage[j]));
+          uses ^= 1u << held_stage[j];
+        }
+        kt_from = kSkew;
+        kt_to = p.k_tiles - kSkew;
+      } else {
+        edge_step(true, k_last == 0);
+      }
+      if (trace && first_mma && lane == 0) trace[kTraceFirstMmaNs] = globaltimer_ns() - trace[kTraceNsStart];
+      first_mma = false;
+      // Middle K steps: the MMAs of the stage, the commit that frees it and a probe
+      // of the next stage's barrier as one instruction sequence of the elected lane.
+      if (fused_ok) {
+        if (w.parts == 1) {
+          for (int kt = kt_from; kt < kt_to; ++kt) {
+            wait_operands();
+            uses ^= 1u << stage;
+            const uint32_t next_stage = next_of(stage);
+            uint32_t probed = 0;
+            if (elect_one_sync()) {
+              probed = umma_kstep4_probe_next<G>(d_tmem0, a_desc, a_desc + b_off0, idesc0, 1u, empty_bar(stage),
+                                                 full_bar(next_stage), (uses >> next_stage) & 1u);
+            }
+            stage_ready = __any_sync(0xffffffffu, probed != 0u);
+            stage = next_stage;
+            a_desc = stage == 0u ? desc0 : a_desc + desc_step;
+          }
+        } else {
+          for (int kt = kt_from; kt < kt_to; ++kt) {
+            wait_operands();
+            uses ^= 1u << stage;
+            const uint32_t next_stage = next_of(stage);
+            uint32_t probed = 0;
+            if (elect_one_sync()) {
+              probed = umma_kstep8_probe_next<G>(d_tmem0, d_tmem1, a_desc, a_desc + b_off0, a_desc + b_off1, idesc0,
+                                                 idesc1, empty_bar(stage), full_bar(next_stage),
+                                                 (uses >> next_stage) & 1u);
+            }
+            stage_ready = __any_sync(0xffffffffu, probed != 0u);
+            stage = next_stage;
+            a_desc = stage == 0u ? desc0 : a_desc + desc_step;
+          }
+        }
+      } else {
+        for (int kt = kt_from; kt < kt_to; ++kt) edge_step(false, false);
+      }
+      if (skewed) {
+        uint32_t held_stage[kSkew];
+        uint64_t held_desc[kSkew];
+        for (int j = 0; j < kSkew; ++j) {  // first part, last kSkew steps
+          wait_operands();
+          stage_ready = false;
+          part_step(0, a_desc, false);
+          held_stage[j] = stage;
+          held_desc[j] = a_desc;
+          stage = next_of(stage);
+          a_desc = stage == 0u ? desc0 : a_desc + desc_step;
+        }
+        if (elect_one_sync()) commit_to(acc_full_bar(slot0));  // first accumulator complete: the epilogue starts on it
+        for (int j = 0; j < kSkew; ++j) {  // second part, last kSkew steps
+          part_step(1, held_desc[j], false);
+          if (elect_one_sync()) commit_to(empty_bar(held_stage[j]));
+          uses ^= 1u << held_stage[j];
+        }
+        if (elect_one_sync()) commit_to(acc_full_bar(slot1));
+      } else if (k_last > 0) {
+        edge_step(false, true);
       }
       acc_it += static_cast<uint32_t>(w.parts);
       // A lane whose wait ran out has raised the abort flag, which makes every

@@ -129,9 +129,22 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait. `abort_flag` is a CTA-shared word any role sets when it
 // gives up; a set flag makes every other wait give up at its next check.
+// `spin` polls with the non-suspending test_wait instead of try_wait (which may
+// park the thread for a hardware-chosen time before it looks again).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile uint32_t* abort_flag,
-                                                  uint64_t timeout_ns) {
+                                                  uint64_t timeout_ns, bool spin = false) {
+  if (spin) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 1;; ++it) {
+      if (mbar_test_wait(bar, parity)) return true;
+      if ((it & 0x3ffu) == 0) {
+        if (*abort_flag != 0u) return false;
+        if (globaltimer_ns() - t0 > timeout_ns) return false;
+      }
+    }
+  }
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {

@@ -6,9 +6,13 @@ projection, next to the kernels timed alone and the whole call.
     python -m torch.distributed.run --nnodes=1 --nproc-per-node U --master-addr 127.0.0.1 \
         --master-port 29545 -m megaup_b200.handoff_profile [--iters 30]
 
-Run it once per hand-off protocol (``MEGA_UP_FUSED_SYNC=1``, the default: the
-hand-offs ride inside the kernels; ``=0``: two stand-alone barrier kernels per
-operation, which then show up inside the second segment of each call). An
+Run it once per hand-off protocol (``MEGA_UP_HANDOFF=lazy``, the default: one
+barrier kernel per operation, the second hand-off signalled from the tail of
+the operation's last kernel; ``folded``: both inside the kernels; ``barriers``:
+two stand-alone barrier kernels per operation; barrier kernels show up inside
+the segment of the launch they precede). The
+report ends with the pull kernel's own trace words over real peers (first panel
+gate of every CTA, first ticket stored, all rows pulled). An
 event between two launches takes away their programmatic overlap, so the
 segments add up to a little more than the call timed as a whole; the
 difference is printed. Every figure is the maximum over the ranks of the
@@ -26,7 +30,7 @@ import torch
 import torch.distributed as dist
 
 import megaup_b200 as mega_up
-from megaup_b200 import runtime as runtime_module
+from megaup_b200 import _native
 
 HIDDEN, HEADS, HEAD_DIM, TOKENS = 5120, 40, 128, 4096
 
@@ -104,7 +108,7 @@ def main() -> None:
     x2d = x.view(TOKENS, HIDDEN)
     report: dict[str, object] = {
         "up": up,
-        "handoff": "folded into the kernels" if runtime_module._FUSED_SYNC else "two barrier kernels per operation",
+        "handoff": runtime.handoff,
     }
     report["peer_write_call_us"] = whole(lambda: writer(x, out=out, validate_group=False))
     report["pull_call_us"] = whole(lambda: puller(hx, validate_group=False))
@@ -128,6 +132,30 @@ def main() -> None:
     report["call_minus_kernel_us"] = {
         "peer_write": report["peer_write_call_us"] - report["peer_write_kernel_alone_us"],
         "pull": report["pull_call_us"] - report["pull_kernel_alone_us"],
+    }
+    # ---- the pull kernel's own trace words over real peers (per CTA; see mup_pull_plan_set_trace)
+    sync_all()
+    trace = torch.zeros((puller.compiled.grid_ctas, 16), dtype=torch.int64, device=device)
+    _native.call("mup_pull_plan_set_trace", puller.compiled._plan, trace.data_ptr())
+    gates, stored, done, kernel = [], [], [], []
+    for _ in range(4):
+        trace.zero_()
+        sync_all()
+        puller(hx, validate_group=False)
+        torch.cuda.synchronize(device)
+        t = trace.cpu().double()
+        first_gate = t[:, 10][t[:, 10] > 0] / 1e3
+        gates.append([float(first_gate.min()), float(first_gate.mean()), float(first_gate.max())])
+        stored.append(float(t[:, 13][t[:, 13] > 0].mean()) / 1e3)
+        done.append(float(t[:, 8].max() - t[:, 6].min()) / 1e3)
+        kernel.append(float(t[:, 7].max() - t[:, 6].min()) / 1e3)
+    _native.call("mup_pull_plan_set_trace", puller.compiled._plan, None)
+    gate_min, gate_mean, gate_max = median_us(gates)
+    report["pull_kernel_trace"] = {
+        "first_gate_open_us_min_mean_max": [gate_min, gate_mean, gate_max],
+        "first_ticket_stored_us": reduce_max([statistics.median(stored)])[0],
+        "all_rows_pulled_us": reduce_max([statistics.median(done)])[0],
+        "kernel_us": reduce_max([statistics.median(kernel)])[0],
     }
     torch.cuda.synchronize(device)
     runtime.check_status()

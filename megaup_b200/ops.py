@@ -553,14 +553,16 @@ class _PeerWriteBase:
     def _launch(self, x: Tensor) -> None:
         rows = _rows(self._kind, self._logical_shape())
         runtime = self.runtime
-        if runtime.fused_sync:
-            # the kernel waits for the slots' owners before its first store and
-            # raises the "written" flag itself when its last CTA is done
-            sync = runtime._next_handoff()
+        if runtime.handoff in ("folded", "lazy"):
+            # the kernel waits for the slots' owners before its first store (they may
+            # still be copying the previous result out); folded: its last CTA also
+            # raises the "written" flag, lazy: a barrier kernel follows instead
+            sync = runtime._sync(wait=True, signal=runtime.handoff == "folded")
             self.launch(x.view(rows, self.in_features), sync=sync, stream_handle=runtime._stream())
             runtime._done_value = int(sync.done_after)
         else:
             self.launch(x.view(rows, self.in_features), stream_handle=runtime._stream())
+        runtime._last_operation = "peer_write"
 
     # phase 2: barrier, slots -> ordinary memory, barrier
     def _materialize(self, out: Tensor) -> None:
@@ -569,7 +571,7 @@ class _PeerWriteBase:
         layout = self._layout()
         if layout is not None:
             runtime.copy_peer_written_indexed(
-                rows=shape[0], index=layout.to_thd_index, out=out, _fused=runtime.fused_sync
+                rows=shape[0], index=layout.to_thd_index, out=out, _managed=True
             )
             return
         # SBHD rows are sequence-major and a THD slab is already in global
@@ -581,7 +583,7 @@ class _PeerWriteBase:
             shard_heads=self._shard_heads,
             head_dim=self.head_dim,
             out=out.view(batch, up * sequence, self._shard_heads, self.head_dim),
-            _fused=runtime.fused_sync,
+            _managed=True,
         )
 
     def __call__(self, x: Tensor, *, out: Tensor | None = None, validate_group: bool = True) -> Tensor:
@@ -992,29 +994,31 @@ class _PullBase:
                 rows=shape[0],
                 source=head_x.view(up * shape[0], self.in_features // up),
                 index=layout.to_source_major_index,
-                _fused=runtime.fused_sync,
+                _managed=True,
             )
             return
         # Rank chunks follow each other along the leading axis for SBHD and a
         # THD slab, so both stage like BSHD with B = 1.
         batch, sequence = (shape[0], shape[1]) if self._kind == "bshd" else (1, _rows(self._kind, shape))
         runtime.stage_head_parallel(
-            head_x.view(batch, up * sequence, shard_heads, self.head_dim), _fused=runtime.fused_sync
+            head_x.view(batch, up * sequence, shard_heads, self.head_dim), _managed=True
         )
 
     # phase 2: pull + GEMM, then barrier so no peer's slot is reused too early
     def _launch(self) -> None:
         runtime = self.runtime
         handle = runtime._stream()
-        if runtime.fused_sync:
-            # the pull workers wait for the peers' staging copies, and the last of
-            # them to finish hands every arena back, long before the GEMM ends
-            sync = runtime._next_handoff()
+        if runtime.handoff in ("folded", "lazy"):
+            # the last pull worker to finish hands every arena back, long before the
+            # GEMM ends; folded: the pull workers also wait for the peers' staging
+            # copies themselves, lazy: a barrier kernel has done that already
+            sync = runtime._sync(wait=runtime.handoff == "folded", signal=True)
             self.compiled(sync=sync, stream_handle=handle)
             runtime._done_value = int(sync.done_after)
         else:
             self.compiled(stream_handle=handle)
             runtime.finish_pull()
+        runtime._last_operation = "pull"
 
     def __call__(self, head_x: Tensor, *, validate_group: bool = True) -> Tensor:
         self._validate_call(head_x, validate_group)

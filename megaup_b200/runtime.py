@@ -46,14 +46,27 @@ SHARD_MULTIPLE = 128
 _CONTROL_BYTES = 4096
 _FLAG_TIMEOUT_NS = int(float(os.environ.get("MEGA_UP_FLAG_TIMEOUT_S", "30")) * 1e9)
 _KERNEL_TIMEOUT_NS = int(float(os.environ.get("MEGA_UP_KERNEL_TIMEOUT_S", "5")) * 1e9)
-# The two slot hand-offs of an operation ride inside its kernels: every kernel
-# of an operation waits for the sync point before it (at its first access to
-# memory the hand-off protects) and its last CTA signals the next one, so an
-# operation is two launches and the "slots may be reused" hand-off is only
-# waited for by the next operation, deep inside its first kernel.
-# MEGA_UP_FUSED_SYNC=0 goes back to two stand-alone barrier kernels per
-# operation (the reference's protocol, runtime.py:264, :281, :415, :421 there).
-_FUSED_SYNC = os.environ.get("MEGA_UP_FUSED_SYNC", "1") == "1"
+# How the two slot hand-offs of an operation ("the slots are written" /
+# "the slots may be reused") are carried out, MEGA_UP_HANDOFF:
+#   lazy      (default) one stand-alone barrier kernel per operation for the
+#             first hand-off; the second is only signalled, by the last CTA of
+#             the operation's last kernel, and waited for by the next operation
+#             where it first touches the slots (deep inside its GEMM, or not at
+#             all when the next operation only rewrites this rank's own slots
+#             after reading them itself);
+#   folded    both hand-offs ride inside the kernels (no barrier launches);
+#   barriers  two stand-alone barrier kernels per operation (the reference's
+#             protocol, runtime.py:264, :281, :415, :421 there).
+# Measured on 2 B200s, Wan2.1-14B projection, us per step (one peer-write and
+# one pull call): barriers 385, folded 401 (every block of a copy kernel polls
+# system-scope flags, and the GEMM tail has to collect all arrivals before the
+# flags go out).
+_HANDOFF = os.environ.get("MEGA_UP_HANDOFF") or {"1": "folded", "0": "barriers"}.get(
+    os.environ.get("MEGA_UP_FUSED_SYNC", ""), "lazy"
+)
+if _HANDOFF not in ("lazy", "folded", "barriers"):
+    raise ValueError(f"MEGA_UP_HANDOFF must be lazy, folded or barriers, got {_HANDOFF!r}")
+_FUSED_SYNC = _HANDOFF == "folded"
 
 
 def _wire_epoch(count: int) -> int:
@@ -269,6 +282,9 @@ class MegaUPRuntime:
     # device-side failures observed so far; pull executables compare it with the
     # count they last saw and zero their counters after a failure
     failure_count: int = field(default=0, init=False, repr=False)
+    # kind of the operation that last used the arena ("peer_write" / "pull"): a
+    # lazily handed-off operation leaves its second sync point to its successor
+    _last_operation: str | None = field(default=None, init=False, repr=False)
 
     @property
     def shard_hidden(self) -> int:
@@ -296,16 +312,23 @@ class MegaUPRuntime:
         return handle if handle is not None else torch.cuda.current_stream(self.device).cuda_stream
 
     @property
+    def handoff(self) -> str:
+        """``"lazy"``, ``"folded"`` or ``"barriers"`` (see ``MEGA_UP_HANDOFF``); an
+        emulated single-process group needs none: its stream order is the hand-off."""
+
+        return "none" if self.emulated else _HANDOFF
+
+    @property
     def fused_sync(self) -> bool:
-        """Whether slot hand-offs ride inside the kernels (multi-process runtimes)."""
+        """Whether both slot hand-offs ride inside the kernels (multi-process runtimes)."""
 
-        return _FUSED_SYNC and not self.emulated
+        return self.handoff == "folded"
 
-    def _next_handoff(self) -> "_native.MupSync":
-        """Hand-off for the next kernel of an operation: it waits for the sync point
-        reached so far and signals the next one. Every operation launches two
-        such kernels (peer-write: GEMM, copy-out; pull: staging copy, GEMM), so
-        an operation still spans two sync points, as with explicit barriers."""
+    def _sync(self, *, wait: bool, signal: bool) -> "_native.MupSync":
+        """Hand-off description for one kernel: ``wait`` for the sync point reached
+        so far before its first access to the slots, ``signal`` the next sync
+        point from its last CTA. Sync points are numbered alike on every rank
+        (every rank issues the same operations in the same order)."""
 
         if self._done_counter is None:
             self._done_counter = torch.zeros(1, dtype=torch.int64, device=self.device)
@@ -314,26 +337,58 @@ class MegaUPRuntime:
             peer_flags=self._flag_array,
             up=self.up,
             rank=self.local_rank,
-            wait_epoch=_wire_epoch(self._epoch),
-            signal_epoch=_wire_epoch(self._epoch + 1),
+            wait_epoch=_wire_epoch(self._epoch) if wait else 0,
+            signal_epoch=_wire_epoch(self._epoch + 1) if signal else 0,
             done_counter=self._done_counter.data_ptr(),
             done_before=self._done_value,
             done_after=0,
             status_device_ptr=self.status_address or None,
             timeout_ns=_FLAG_TIMEOUT_NS,
         )
-        self._epoch += 1
+        if signal:
+            self._epoch += 1
         return sync
 
-    def _copy(self, name: str, *args: object, fused: bool) -> None:
-        """Launch a layout copy, with the hand-off folded in when ``fused``."""
+    def _next_handoff(self) -> "_native.MupSync":
+        """Folded protocol: the next kernel of an operation waits for the sync point
+        reached so far and signals the next one. Every operation launches two
+        such kernels (peer-write: GEMM, copy-out; pull: staging copy, GEMM), so
+        an operation still spans two sync points, as with explicit barriers."""
 
-        if not fused:
+        return self._sync(wait=True, signal=True)
+
+    def _copy(self, name: str, *args: object, sync: "_native.MupSync | None" = None) -> None:
+        """Launch a layout copy, with a hand-off folded in when ``sync`` is given."""
+
+        if sync is None:
             _native.call(name, *args, self._stream())
             return
-        sync = self._next_handoff()
         _native.call(name + "_synced", *args, self._stream(), ctypes.byref(sync))
         self._done_value = int(sync.done_after)
+
+    def _copy_out_sync(self) -> "_native.MupSync | None":
+        """Hand-off of a copy-out of peer-written slots, after the barrier (if any)
+        this call also issues: folded waits and signals inside the copy, lazy
+        has a barrier kernel in front and only signals from the copy's tail."""
+
+        if self.handoff == "folded":
+            return self._sync(wait=True, signal=True)
+        if self.handoff == "lazy":
+            self.barrier()
+            return self._sync(wait=False, signal=True)
+        return None
+
+    def _stage_sync(self) -> "_native.MupSync | None":
+        """Hand-off of a staging copy into this rank's own slots. Lazy: the peers
+        must have finished pulling the previous contents, which only a previous
+        PULL leaves open (after a peer-write this rank read the slots itself,
+        earlier on this stream)."""
+
+        if self.handoff == "folded":
+            return self._sync(wait=True, signal=True)
+        if self.handoff == "lazy" and self._last_operation == "pull":
+            return self._sync(wait=True, signal=False)
+        return None
 
     def check_status(self) -> None:
         """Raise if a kernel of an earlier operation gave up on a bounded wait.
@@ -449,18 +504,18 @@ class MegaUPRuntime:
 
     def _regroup(
         self, dst: Tensor, src: Tensor, batch: int, sequence: int, shard: int, to_batch_major: bool,
-        fused: bool = False,
+        sync: "_native.MupSync | None" = None,
     ) -> None:
         if batch == 1:
             # source-major and batch-major coincide: one straight copy
             self._copy(
                 "mup_gather_rows", dst.data_ptr(), src.data_ptr(), None, self.up * sequence, shard,
-                fused=fused,
+                sync=sync,
             )
         else:
             self._copy(
                 "mup_regroup_rows", dst.data_ptr(), src.data_ptr(), self.up, batch, sequence, shard,
-                1 if to_batch_major else 0, fused=fused,
+                1 if to_batch_major else 0, sync=sync,
             )
 
     def copy_peer_written(
@@ -471,12 +526,12 @@ class MegaUPRuntime:
         shard_heads: int,
         head_dim: int,
         out: Tensor | None = None,
-        _fused: bool = False,
+        _managed: bool = False,
     ) -> Tensor:
         """Materialize compact peer writes as ``[B,UP*S,H/UP,D]``: barrier,
-        copy, barrier (reference: runtime.py:227-282). With ``_fused`` (used by
-        the prepared executables on a multi-process runtime) the copy kernel
-        itself waits for the peers' writes and hands the slots back."""
+        copy, barrier (reference: runtime.py:227-282). ``_managed`` (used by the
+        prepared executables) follows the runtime's hand-off protocol instead:
+        the copy kernel then hands the slots back from its last block."""
 
         rows = int(batch) * int(sequence)
         shard = int(shard_heads) * int(head_dim)
@@ -494,8 +549,8 @@ class MegaUPRuntime:
             raise ValueError(
                 f"out must be a contiguous BF16 tensor on the runtime device with shape {expected}"
             )
-        if _fused:
-            self._regroup(out, self.slots(rows, width), batch, sequence, shard, True, fused=True)
+        if _managed and self.handoff in ("folded", "lazy"):
+            self._regroup(out, self.slots(rows, width), batch, sequence, shard, True, sync=self._copy_out_sync())
             return out
         self.barrier()
         self._regroup(out, self.slots(rows, width), batch, sequence, shard, True)
@@ -517,7 +572,7 @@ class MegaUPRuntime:
             )
 
     def copy_peer_written_indexed(
-        self, *, rows: int, index: Tensor, out: Tensor, _fused: bool = False
+        self, *, rows: int, index: Tensor, out: Tensor, _managed: bool = False
     ) -> Tensor:
         """Output row ``i`` receives source-major arena row ``index[i]``
         (reference: runtime.py:298-337)."""
@@ -538,16 +593,16 @@ class MegaUPRuntime:
         shard = out.numel() // total
         self.check_capacity(rows, self.up * shard)
         args = (out.data_ptr(), self.slots(rows, self.up * shard).data_ptr(), index.data_ptr(), total, shard)
-        if _fused:
-            self._copy("mup_gather_rows", *args, fused=True)
+        if _managed and self.handoff in ("folded", "lazy"):
+            self._copy("mup_gather_rows", *args, sync=self._copy_out_sync())
             return out
         self.barrier()
-        self._copy("mup_gather_rows", *args, fused=False)
+        self._copy("mup_gather_rows", *args)
         self.barrier()
         return out
 
     def stage_rows_indexed(
-        self, *, rows: int, source: Tensor, index: Tensor, _fused: bool = False
+        self, *, rows: int, source: Tensor, index: Tensor, _managed: bool = False
     ) -> None:
         """Slot row ``(d, j)`` receives ``source[index[d*rows + j]]``, then
         barrier (reference: runtime.py:339-373)."""
@@ -568,12 +623,12 @@ class MegaUPRuntime:
         shard = int(source.shape[1])
         self._copy(
             "mup_gather_rows", self.slots(rows, self.up * shard).data_ptr(), source.data_ptr(),
-            index.data_ptr(), total, shard, fused=_fused,
+            index.data_ptr(), total, shard, sync=self._stage_sync() if _managed else None,
         )
-        if not _fused:
+        if not (_managed and self.handoff == "folded"):
             self.barrier()
 
-    def stage_head_parallel(self, tensor: Tensor, _fused: bool = False) -> tuple[int, int, int, int]:
+    def stage_head_parallel(self, tensor: Tensor, _managed: bool = False) -> tuple[int, int, int, int]:
         """Stage ``[B,UP*S,H/UP,D]`` as ``[destination, B*S, H/UP*D]`` slots,
         then barrier (reference: runtime.py:375-416)."""
 
@@ -589,8 +644,11 @@ class MegaUPRuntime:
         sequence = global_sequence // self.up
         shard = shard_heads * head_dim
         rows = batch * sequence
-        self._regroup(self.slots(rows, self.up * shard), tensor, batch, sequence, shard, False, fused=_fused)
-        if not _fused:
+        self._regroup(
+            self.slots(rows, self.up * shard), tensor, batch, sequence, shard, False,
+            sync=self._stage_sync() if _managed else None,
+        )
+        if not (_managed and self.handoff == "folded"):
             self.barrier()
         return batch, sequence, shard_heads, head_dim
 

@@ -20,10 +20,11 @@ def _group_size() -> int:
     return 8 if count >= 8 else 4 if count >= 4 else 2 if count >= 2 else 0
 
 
-@pytest.mark.parametrize("handoff", ["folded_into_kernels", "barrier_kernels"])
+@pytest.mark.parametrize("handoff", ["lazy", "folded", "barriers"])
 def test_fused_operators_match_cublas_plus_nccl(handoff: str) -> None:
-    """Both slot hand-off protocols: the hand-off folded into the producing / consuming
-    kernels (the default) and two stand-alone barrier kernels per operation. The run
+    """Every slot hand-off protocol: one barrier kernel per operation with the second
+    hand-off left to the next operation (the default), both hand-offs folded into the
+    kernels, and two stand-alone barrier kernels per operation. The run
     covers every layout, the reference's multi-GPU shape matrix for this group size,
     the collective rejections, a hand-off that times out, and (--full) the
     Wan2.1-14B, Llama-3-8B, Llama-3-70B and edge-shape configurations on real peers."""
@@ -33,7 +34,7 @@ def test_fused_operators_match_cublas_plus_nccl(handoff: str) -> None:
     up = _group_size()
     if up == 0:
         pytest.skip("needs at least 2 GPUs")
-    env = dict(os.environ, MEGA_UP_FUSED_SYNC="1" if handoff == "folded_into_kernels" else "0")
+    env = dict(os.environ, MEGA_UP_HANDOFF=handoff)
     command = [
         sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={up}",
         "--master-addr", "127.0.0.1", "--master-port", "29533", str(ROOT / "tests" / "run_distributed.py"),
