@@ -643,10 +643,10 @@ def main() -> None:
                 "steps": soak,
             },
             # per step: GEMM + copy-out, staging copy + GEMM, plus the barrier kernels of the hand-off protocol
-            "gpu_launches": args.steps * {"none": 4, "folded": 4, "lazy": 6, "barriers": 8}[runtime.handoff],
+            "gpu_launches": args.steps * {"none": 4, "folded": 4, "lazy": 7, "barriers": 8}[runtime.handoff],
             "handoff": {
                 "none": "emulated peers on one stream",
-                "lazy": "one barrier kernel per operation, second hand-off signalled from the last kernel's tail",
+                "lazy": "barrier kernels, except a pull's second hand-off: signalled by its last pull warp, awaited inside the next operation",
                 "folded": "both hand-offs folded into the kernels",
                 "barriers": "two barrier kernels per operation",
             }[runtime.handoff],

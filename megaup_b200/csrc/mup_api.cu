@@ -221,9 +221,11 @@ int query_device(int device, DeviceInfo* info) {
 
 template <int G, int MODE>
 int configure_kernel(int* max_clusters) {
-  auto kernel = mup::fused_exchange_gemm_kernel<G, MODE>;
+  auto kernel = mup::fused_exchange_gemm_kernel<G, MODE, true>;
   const int smem = mup::GemmCfg<G>::kSmemBytes;
   MUP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  MUP_CUDA(cudaFuncSetAttribute(mup::fused_exchange_gemm_kernel<G, MODE, false>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   if (G == 2) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -264,7 +266,9 @@ bool pdl_enabled() {
 
 template <int G, int MODE>
 int launch_kernel(const mup::GemmParams& params, int grid, cudaStream_t stream) {
-  auto kernel = mup::fused_exchange_gemm_kernel<G, MODE>;
+  // lists without two-accumulator items run the instantiation without their code
+  auto kernel = params.max_item_cols > mup::kBlockN ? mup::fused_exchange_gemm_kernel<G, MODE, true>
+                                                    : mup::fused_exchange_gemm_kernel<G, MODE, false>;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid, 1, 1);
@@ -357,10 +361,12 @@ int check_common(int device, int rows, int n, int k, int up, int rank, const voi
 // stages in flight cover only partly (measured per K step: 128-wide 410 with 8
 // stages, 192-wide 530 with 7, 256-wide 565-585 with 6). An item costs 1200
 // cycles on top (pipeline fill, accumulator hand-over); an item of two
-// accumulators (wider than 256 columns) 6500, because all of TMEM belongs to it
-// and the K loop of the next item cannot start before the epilogue has read an
-// accumulator; a change of stage geometry between two items of a CTA costs
-// another 3000.
+// accumulators (wider than 256 columns) 15000, because all of TMEM belongs to
+// it and the K loop of the next item cannot start before the epilogue has read
+// an accumulator (with that figure the model reproduces what was measured: two
+// accumulators lose at K = 4096 and 5120 and win at K = 8192, where the
+// 16384 x 8192 x 8192 pull runs 10 % faster with 512-wide items); a change of
+// stage geometry between two items of a CTA costs another 3000.
 // Candidates: every M tile cut into q equal items, for a range of q; lists of
 // r * slots items for a few r, where the M tiles differ by at most one item; and
 // each of those with the items of a partly filled last round cut into f pieces
@@ -390,20 +396,43 @@ struct Schedule {
 };
 
 // Load latency the stages in flight have to cover, in SM cycles (about 1.8 us:
-// every K step touches lines no SM has read in this round of items).
+// every K step touches lines no SM has read in this round of items). While the
+// pull warps of a pull launch keep the memory system busy the operand loads
+// take longer; with 4500 the model picks what was measured on
+// 4096 x 5120 x 5120: 256-wide items for the peer-write kernel (148.5 against
+// 150 us for 512-wide), 512-wide items for the pull kernel (162.7 against
+// 168.3 us).
 constexpr double kModelLoadLatency = 3000.0;
+constexpr double kModelLoadLatencyWhilePulling = 4500.0;
 
-double item_cycles(int units, int k_tiles, int g) {
+// What the time model needs to know beside an item's width.
+struct ModelShape {
+  int k_tiles = 1;
+  int g = 2;
+  double latency = kModelLoadLatency;
+  bool narrow_class = true;  // items of at most 128 columns get the 8-stage geometry
+};
+
+double item_cycles(int units, const ModelShape& shape) {
   const int cols = units * mup::kUnit;
   const double tensor = 2.0 * cols;
-  const int stages = mup::tile_stages(mup::stage_class_cols(cols), g);
-  const double step = std::max(tensor, (kModelLoadLatency + tensor) / stages);
-  const double fixed = cols > mup::kBlockN ? 6500.0 : 1200.0;
-  return k_tiles * step + fixed;
+  const int stages = mup::tile_stages(mup::stage_class_cols(cols, shape.narrow_class), shape.g);
+  const double step = std::max(tensor, (shape.latency + tensor) / stages);
+  const double fixed = cols > mup::kBlockN ? 15000.0 : 1200.0;
+  return shape.k_tiles * step + fixed;
 }
 
 int item_stage_class(uint32_t e) {
-  return mup::stage_class_cols((static_cast<int>((e >> 26) & 0x7u) + 1) * mup::kUnit);
+  // lists that change geometry have wide items; their narrow items use the 256-column one
+  return mup::stage_class_cols((static_cast<int>((e >> 26) & 0x7u) + 1) * mup::kUnit, false);
+}
+
+// The 128-column stage geometry (8 stages) is used only by lists made of such
+// items alone; see kFlagNoNarrowClass.
+bool list_uses_narrow_class(const std::vector<uint32_t>& items) {
+  for (uint32_t e : items)
+    if (e != mup::kNoItem && ((e >> 26) & 0x7u) + 1u > 2u) return false;
+  return true;
 }
 
 // Items of one M tile: `q` items covering `units` 64-column units, the first
@@ -418,21 +447,22 @@ void emit_row(std::vector<uint32_t>* out, int m_idx, int units, int q, int start
   }
 }
 
-double list_item_cycles(uint32_t e, int k_tiles, int g) {
+double list_item_cycles(uint32_t e, const ModelShape& shape) {
   if (e == mup::kNoItem) return 0.0;
-  return item_cycles(static_cast<int>((e >> 26) & 0x7u) + 1, k_tiles, g);
+  return item_cycles(static_cast<int>((e >> 26) & 0x7u) + 1, shape);
 }
 
-double critical_path(const std::vector<uint32_t>& items, int slots, int k_tiles, int g) {
+double critical_path(const std::vector<uint32_t>& items, int slots, ModelShape shape) {
   std::vector<double> load(static_cast<size_t>(slots), 0.0);
   std::vector<int> last_class(static_cast<size_t>(slots), 0);
+  shape.narrow_class = list_uses_narrow_class(items);
   for (size_t i = 0; i < items.size(); ++i) {
     if (items[i] == mup::kNoItem) continue;
     const size_t c = i % static_cast<size_t>(slots);
-    load[c] += list_item_cycles(items[i], k_tiles, g);
+    load[c] += list_item_cycles(items[i], shape);
     // a change of stage geometry between two items drains the pipeline once
     const int cls = item_stage_class(items[i]);
-    if (last_class[c] != 0 && last_class[c] != cls) load[c] += kModelLoadLatency;
+    if (last_class[c] != 0 && last_class[c] != cls) load[c] += shape.latency;
     last_class[c] = cls;
   }
   return *std::max_element(load.begin(), load.end());
@@ -442,9 +472,10 @@ double critical_path(const std::vector<uint32_t>& items, int slots, int k_tiles,
 // work so far gets the cheapest item of the round; a partly filled last round
 // goes to the least loaded slots and the others get kNoItem. The first round
 // keeps list order (in pull mode its items are the first panels to arrive).
-void balance_rounds(std::vector<uint32_t>* items, int slots, int k_tiles, int g, double start_cycles_per_m_tile) {
+void balance_rounds(std::vector<uint32_t>* items, int slots, ModelShape shape, double start_cycles_per_m_tile) {
   const size_t n = items->size();
   if (n <= static_cast<size_t>(slots)) return;
+  shape.narrow_class = list_uses_narrow_class(*items);
   std::vector<double> load(static_cast<size_t>(slots), 0.0);
   // Pull mode: a CTA pair cannot start before the rows of its first item have
   // arrived, and rows arrive in ascending order at the rate the peers deliver
@@ -471,14 +502,14 @@ void balance_rounds(std::vector<uint32_t>* items, int slots, int k_tiles, int g,
                        [&](int a, int b) { return load[static_cast<size_t>(a)] > load[static_cast<size_t>(b)]; });
       // cheapest item first; ties keep list order
       std::stable_sort(round.begin(), round.end(), [&](uint32_t a, uint32_t b) {
-        return list_item_cycles(a, k_tiles, g) < list_item_cycles(b, k_tiles, g);
+        return list_item_cycles(a, shape) < list_item_cycles(b, shape);
       });
       // with fewer items than slots the most loaded slots sit the round out
       const size_t skip = static_cast<size_t>(slots) - count;
       for (size_t i = 0; i < count; ++i) placed[static_cast<size_t>(order[skip + i])] = round[i];
     }
     for (int c = 0; c < slots; ++c) {
-      load[static_cast<size_t>(c)] += list_item_cycles(placed[static_cast<size_t>(c)], k_tiles, g);
+      load[static_cast<size_t>(c)] += list_item_cycles(placed[static_cast<size_t>(c)], shape);
       out.push_back(placed[static_cast<size_t>(c)]);
     }
   }
@@ -492,8 +523,7 @@ struct ListOptions {
   bool rotate = false;  // peer-write: each rank starts every M tile at its own column block
   int band = 1;
   int slots = 1;
-  int k_tiles = 1;
-  int g = 2;
+  ModelShape shape;
   double start_cycles_per_m_tile = 0.0;
 };
 
@@ -543,8 +573,8 @@ Schedule build_list(const std::vector<int>& q_of_row, const ListOptions& o, int 
   s.max_cols = 0;
   for (uint32_t e : s.items) s.max_cols = std::max(s.max_cols, (static_cast<int>((e >> 26) & 0x7u) + 1) * mup::kUnit);
   if (env_int("MEGA_UP_BALANCE", 1) != 0)
-    balance_rounds(&s.items, o.slots, o.k_tiles, o.g, o.start_cycles_per_m_tile);
-  s.critical_cycles = critical_path(s.items, o.slots, o.k_tiles, o.g);
+    balance_rounds(&s.items, o.slots, o.shape, o.start_cycles_per_m_tile);
+  s.critical_cycles = critical_path(s.items, o.slots, o.shape);
   return s;
 }
 
@@ -554,14 +584,18 @@ Schedule choose_schedule(int mode, int m_tiles, int n, int k_tiles, int up, int 
   o.up = up;
   o.rank = rank;
   o.rotate = (mode == mup::MODE_PEER_WRITE);
-  // Peer-write lists walk bands of 16 M tiles column by column (148.9 against
-  // 150.7 us for 4096 x 5120 x 5120: the CTA pairs of a round then share W boxes
-  // rather than A boxes); pull lists stay row by row, the order in which the
-  // pulled rows arrive.
-  o.band = o.rotate ? std::max(1, env_int("MEGA_UP_BAND", 16)) : 1;
+  // MEGA_UP_BAND=b makes a peer-write list walk bands of b M tiles column by
+  // column. With emulated peers b = 16 measured 148.9 against 150.7 us for
+  // 4096 x 5120 x 5120 (the CTA pairs of a round share W boxes rather than A
+  // boxes), but over NVLink all CTA pairs then store into the same peer at the
+  // same time and the kernel slowed from 155 to 162 us on two GPUs: row by row
+  // (every round spreads over all destinations) is the default.
+  o.band = o.rotate ? std::max(1, env_int("MEGA_UP_BAND", 1)) : 1;
   o.slots = slots;
-  o.k_tiles = k_tiles;
-  o.g = g;
+  o.shape.k_tiles = k_tiles;
+  o.shape.g = g;
+  o.shape.latency = (mode == mup::MODE_PULL && up > 1) ? kModelLoadLatencyWhilePulling : kModelLoadLatency;
+  if (const char* env = getenv("MEGA_UP_MODEL_LATENCY")) o.shape.latency = atof(env);
   const int units = o.units;
   const int max_units = mup::max_item_cols(g) / mup::kUnit;
   const int q_min = (units + max_units - 1) / max_units;
@@ -687,7 +721,8 @@ int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int 
   }
   core->device_items = table;
   p.items = static_cast<const uint32_t*>(table);
-  if (const char* env = getenv("MEGA_UP_KERNEL_FLAGS")) p.flags = static_cast<unsigned int>(atoi(env));
+  if (!list_uses_narrow_class(core->host_items)) p.flags |= mup::kFlagNoNarrowClass;
+  if (const char* env = getenv("MEGA_UP_KERNEL_FLAGS")) p.flags ^= static_cast<unsigned int>(atoi(env));
   return MUP_OK;
 }
 
@@ -842,7 +877,7 @@ __global__ void load_latency_kernel(const unsigned long long* __restrict__ ptr, 
 // The two copies with the hand-off folded in: every block waits (thread 0
 // polls this rank's flags) before it touches the slots, and counts itself in
 // after its last store; the last block raises the flags at the peers.
-__global__ void gather_rows_synced_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
+__global__ void __launch_bounds__(1024) gather_rows_synced_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
                                           const int64_t* __restrict__ index, int64_t rows,
                                           int64_t vecs, mup::SyncParams sp) {
   mup::grid_dep_launch();
@@ -864,7 +899,7 @@ __global__ void gather_rows_synced_kernel(uint4* __restrict__ dst, const uint4* 
   if (threadIdx.x == 0) mup::sync_arrive_and_signal(sp);
 }
 
-__global__ void regroup_rows_synced_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
+__global__ void __launch_bounds__(1024) regroup_rows_synced_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
                                            int up, int batch, int64_t seq, int64_t vecs,
                                            int to_batch_major, mup::SyncParams sp) {
   mup::grid_dep_launch();
@@ -898,9 +933,6 @@ __global__ void regroup_rows_synced_kernel(uint4* __restrict__ dst, const uint4*
   if (threadIdx.x == 0) mup::sync_arrive_and_signal(sp);
 }
 
-// Grid of a copy that carries a hand-off: at most the blocks that are resident
-// at once (8 x 256 threads per SM), so that every block's wait is paid once,
-// concurrently, and the arrival counter sees few atomics.
 int device_sm_count() {
   // the copies run on the current device; cache its SM count per device ordinal
   static int cached[64] = {0};
@@ -914,9 +946,15 @@ int device_sm_count() {
   return cached[device];
 }
 
+// Grid of a copy that carries a hand-off: blocks of 1024 threads, at most two
+// per SM, so that all of them are resident at once (every block's wait is paid
+// once, concurrently) and the arrival counter sees a few hundred atomics, not
+// thousands: same-address atomics take about 8 ns each, and the blocks of a
+// copy all finish at about the same time.
+constexpr int kSyncedCopyThreads = 1024;
 int synced_copy_grid(int64_t total_vecs) {
-  int64_t blocks = (total_vecs + 255) / 256;
-  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 8;
+  int64_t blocks = (total_vecs + kSyncedCopyThreads - 1) / kSyncedCopyThreads;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 2;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return static_cast<int>(blocks);
@@ -1527,9 +1565,13 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
     const int q_min = (units + max_units - 1) / max_units;
     int best_q = q_min;
     double best_cost = -1.0;
+    ModelShape shape;
+    shape.k_tiles = p.k_tiles;
+    shape.g = g;
+    shape.latency = up > 1 ? kModelLoadLatencyWhilePulling : kModelLoadLatency;
     for (int q = q_min; q <= units; ++q) {
       const long long rounds = (static_cast<long long>(m_tiles) * q + slots - 1) / slots;
-      const double cost = rounds * item_cycles((units + q - 1) / q, p.k_tiles, g);
+      const double cost = rounds * item_cycles((units + q - 1) / q, shape);
       if (best_cost < 0.0 || cost < best_cost * 0.999) {
         best_cost = cost;
         best_q = q;
@@ -1601,7 +1643,7 @@ int mup_gather_rows_synced(void* dst, const void* src, const int64_t* index, int
   mup::SyncParams sp;
   int rc = fill_sync(&sp, sync, static_cast<unsigned long long>(grid));
   if (rc != MUP_OK) return rc;
-  MUP_CUDA(launch_small(gather_rows_synced_kernel, grid, 256, static_cast<cudaStream_t>(stream),
+  MUP_CUDA(launch_small(gather_rows_synced_kernel, grid, kSyncedCopyThreads, static_cast<cudaStream_t>(stream),
                         static_cast<uint4*>(dst), static_cast<const uint4*>(src), index, rows, vecs, sp));
   return MUP_OK;
 }
@@ -1619,7 +1661,7 @@ int mup_regroup_rows_synced(void* dst, const void* src, int up, int batch, int64
   mup::SyncParams sp;
   int rc = fill_sync(&sp, sync, static_cast<unsigned long long>(grid));
   if (rc != MUP_OK) return rc;
-  MUP_CUDA(launch_small(regroup_rows_synced_kernel, grid, 256, static_cast<cudaStream_t>(stream),
+  MUP_CUDA(launch_small(regroup_rows_synced_kernel, grid, kSyncedCopyThreads, static_cast<cudaStream_t>(stream),
                         static_cast<uint4*>(dst), static_cast<const uint4*>(src), up, batch, seq, vecs,
                         to_batch_major, sp));
   return MUP_OK;

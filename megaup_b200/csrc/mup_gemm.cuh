@@ -205,7 +205,11 @@ constexpr unsigned int kFlagSplitCommit = 1u;  // G=2: one commit per CTA of the
 constexpr unsigned int kFlagSeparateIssue = 2u;  // tuning: poll, MMAs and commit as separate statements (the slower issue loop)
 constexpr unsigned int kFlagPullExtraFence = 16u;  // tuning: an explicit fence.acq_rel.gpu before every release of a ready count
 constexpr unsigned int kFlagSpinWaits = 256u;  // tuning: the TMA producer and the MMA warp poll their barriers with test_wait
-constexpr unsigned int kFlagNoNarrowClass = 128u;  // tuning: items of at most 128 columns use the 256-column stage geometry
+// Items of at most 128 columns use the 256-column stage geometry. The host sets
+// it for every list that also has wider items: changing the geometry drains
+// the pipeline, which cost more (0.7-1.0 us on 4096 x 5120 x 5120) than two
+// more stages gain for one short round of narrow items.
+constexpr unsigned int kFlagNoNarrowClass = 128u;
 constexpr unsigned int kFlagNoPartSkew = 64u;   // tuning: two-accumulator items without the skew between their parts
 constexpr unsigned int kFlagNoWPrefetch = 32u;  // tuning: pull mode, do not load W ahead of a closed panel gate
 
@@ -360,9 +364,15 @@ __device__ __forceinline__ WorkItem decode_entry(uint32_t e) {
   return w;
 }
 
-template <int G, int MODE>
+// WIDE = false is the kernel for lists whose items all have one accumulator (at
+// most 256 columns): the code of the two-accumulator items is compiled out.
+// Merely having that code in the kernel slowed single-accumulator items by
+// 2.5 % (186.4 k against 181.6 k cycles per CTA for four rounds of 256-wide
+// items), so each kind of list gets its own instantiation.
+template <int G, int MODE, bool WIDE>
 __global__ void __launch_bounds__(kernel_threads(MODE), 1)
 fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
+  constexpr bool kAllowWide = WIDE;
   using Cfg = GemmCfg<G>;
   extern __shared__ __align__(1024) uint8_t smem[];
 
@@ -468,8 +478,9 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         const int item_cols = w.part_cols[0] + w.part_cols[1];
         const uint32_t item_bytes = static_cast<uint32_t>(tile_stage_bytes(item_cols, G));
         const bool narrow_class = (p.flags & kFlagNoNarrowClass) == 0u;
+        const int class_of_cols = item_cols;
         const uint32_t class_bytes =
-            static_cast<uint32_t>(tile_stage_bytes(stage_class_cols(item_cols, narrow_class), G));
+            static_cast<uint32_t>(tile_stage_bytes(stage_class_cols(class_of_cols, narrow_class), G));
         if (class_bytes != stage_bytes) {
           // Another stage geometry: wait until every stage of the old ring has been
           // consumed (the new stages overlap them), then start over at stage 0.
@@ -481,7 +492,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
           if (!ok) break;
           stage_bytes = class_bytes;
-          num_stages = tile_stages(stage_class_cols(item_cols, narrow_class), G);
+          num_stages = tile_stages(stage_class_cols(class_of_cols, narrow_class), G);
           stage = 0;
           in_flight = 0;
         }
@@ -510,7 +521,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         const int rows0 = tile_b_rows(w.part_cols[0], G);
         const CUtensorMap* const map0 = &p.map_b[w.part_cols[0] / kUnit - 1];
         const int w_row0 = w.n0 + static_cast<int>(cta_rank) * rows0;
-        const bool two_parts = (w.parts == 2);
+        const bool two_parts = kAllowWide && (w.parts == 2);
         const int rows1 = two_parts ? tile_b_rows(w.part_cols[1], G) : 0;
         const CUtensorMap* const map1 = &p.map_b[two_parts ? w.part_cols[1] / kUnit - 1 : 0];
         const int w_row1 = w.n0 + w.part_cols[0] + static_cast<int>(cta_rank) * rows1;
@@ -633,10 +644,10 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
   // run by a single lane inside a divergent branch, ~560 for the warp-uniform
   // loop with poll, four MMAs and commit as separate statements, 512 for the
   // fused sequence used here (umma_kstep4_probe_next / umma_kstep8_probe_next),
-  // which also keeps the pipe full at N = 128. The first and the last K step of
-  // an item use separate statements: the first waits for each accumulator slot
-  // just before the MMAs that overwrite it, the last publishes each part's
-  // accumulator as soon as that part's MMAs are issued.
+  // which also keeps the pipe full at N = 128. Every K step of an item goes
+  // through the fused sequence (separate statements for its first and last step
+  // measured 3800 cycles, a whole pipeline refill, per item boundary), except
+  // the skewed first and last steps of an item of two accumulators.
   if (warp == 1 && !misaligned && cta_rank == 0) {
     const uint64_t desc0 = make_kmajor_sw128_desc(smem_base);
     const bool pair_commit = (G == 2) && (p.flags & kFlagSplitCommit) == 0u;
@@ -776,9 +787,9 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       // in ascending order.
       constexpr int kSkew = 2;
       const int k_last = p.k_tiles - 1;
-      const bool skewed = w.parts == 2 && fused_ok && p.k_tiles >= 2 * kSkew + 2 && num_stages > kSkew &&
+      const bool skewed = kAllowWide && w.parts == 2 && fused_ok && p.k_tiles >= 2 * kSkew + 2 && num_stages > kSkew &&
                           (p.flags & kFlagNoPartSkew) == 0u;
-      int kt_from = 1, kt_to = k_last;  // middle steps [kt_from, kt_to)
+      int kt_from = 0, kt_to = p.k_tiles;  // K steps [kt_from, kt_to) run as fused sequences
       if (skewed) {
         uint32_t held_stage[kSkew];
         uint64_t held_desc[kSkew];
@@ -800,23 +811,23 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
         kt_from = kSkew;
         kt_to = p.k_tiles - kSkew;
-      } else {
-        edge_step(true, k_last == 0);
+      } else if (fused_ok) {
+        // The epilogue must have read the previous contents of the slots this item overwrites.
+        wait_slot(0);
+        if (kAllowWide && w.parts == 2) wait_slot(1);
       }
-      if (trace && first_mma && lane == 0) trace[kTraceFirstMmaNs] = globaltimer_ns() - trace[kTraceNsStart];
-      first_mma = false;
-      // Middle K steps: the MMAs of the stage, the commit that frees it and a probe
-      // of the next stage's barrier as one instruction sequence of the elected lane.
+      // The MMAs of a stage, the commit that frees it and a probe of the next
+      // stage's barrier as one instruction sequence of the elected lane.
       if (fused_ok) {
-        if (w.parts == 1) {
+        if (!kAllowWide || w.parts == 1) {
           for (int kt = kt_from; kt < kt_to; ++kt) {
             wait_operands();
             uses ^= 1u << stage;
             const uint32_t next_stage = next_of(stage);
             uint32_t probed = 0;
             if (elect_one_sync()) {
-              probed = umma_kstep4_probe_next<G>(d_tmem0, a_desc, a_desc + b_off0, idesc0, 1u, empty_bar(stage),
-                                                 full_bar(next_stage), (uses >> next_stage) & 1u);
+              probed = umma_kstep4_probe_next<G>(d_tmem0, a_desc, a_desc + b_off0, idesc0, kt > 0 ? 1u : 0u,
+                                                 empty_bar(stage), full_bar(next_stage), (uses >> next_stage) & 1u);
             }
             stage_ready = __any_sync(0xffffffffu, probed != 0u);
             stage = next_stage;
@@ -830,7 +841,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
             uint32_t probed = 0;
             if (elect_one_sync()) {
               probed = umma_kstep8_probe_next<G>(d_tmem0, d_tmem1, a_desc, a_desc + b_off0, a_desc + b_off1, idesc0,
-                                                 idesc1, empty_bar(stage), full_bar(next_stage),
+                                                 idesc1, kt > 0 ? 1u : 0u, empty_bar(stage), full_bar(next_stage),
                                                  (uses >> next_stage) & 1u);
             }
             stage_ready = __any_sync(0xffffffffu, probed != 0u);
@@ -839,8 +850,10 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
         }
       } else {
-        for (int kt = kt_from; kt < kt_to; ++kt) edge_step(false, false);
+        for (int kt = 0; kt < p.k_tiles; ++kt) edge_step(kt == 0, kt == k_last);
       }
+      if (trace && first_mma && lane == 0) trace[kTraceFirstMmaNs] = globaltimer_ns() - trace[kTraceNsStart];
+      first_mma = false;
       if (skewed) {
         uint32_t held_stage[kSkew];
         uint64_t held_desc[kSkew];
@@ -860,10 +873,14 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
           uses ^= 1u << held_stage[j];
         }
         if (elect_one_sync()) commit_to(acc_full_bar(slot1));
-      } else if (k_last > 0) {
-        edge_step(false, true);
+      } else if (fused_ok) {
+        // Publish the finished accumulators to the epilogue warps.
+        if (elect_one_sync()) {
+          commit_to(acc_full_bar(slot0));
+          if (kAllowWide && w.parts == 2) commit_to(acc_full_bar(slot1));
+        }
       }
-      acc_it += static_cast<uint32_t>(w.parts);
+      acc_it += static_cast<uint32_t>(kAllowWide ? w.parts : 1);
       // A lane whose wait ran out has raised the abort flag, which makes every
       // later wait return at once; the warp leaves together at an item boundary.
       if (__any_sync(0xffffffffu, failed)) break;
@@ -894,7 +911,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       if (w.parts == 0) continue;
       const int row0 = (w.m_idx * G + static_cast<int>(cta_rank)) * kBlockM + q * kEpiRows;
       int part_col0 = w.n0;
-      for (int part = 0; part < w.parts && ok; ++part, ++acc_it) {
+      for (int part = 0; part < (kAllowWide ? w.parts : 1) && ok; ++part, ++acc_it) {
         const uint32_t as = acc_it & 1u;
         const uint32_t aphase = (acc_it >> 1) & 1u;
         // The bias of a 64-column sub-tile is fetched one sub-tile ahead (here: before the

@@ -426,15 +426,17 @@ __device__ __forceinline__ uint32_t umma_kstep4_probe_next(uint32_t d_tmem, uint
 template <int G>
 __device__ __forceinline__ uint32_t umma_kstep8_probe_next(uint32_t d_tmem0, uint32_t d_tmem1, uint64_t a_desc,
                                                            uint64_t b_desc0, uint64_t b_desc1, uint32_t idesc0,
-                                                           uint32_t idesc1, uint32_t commit_bar,
-                                                           uint32_t next_full_bar, uint32_t next_parity) {
+                                                           uint32_t idesc1, uint32_t accumulate_first,
+                                                           uint32_t commit_bar, uint32_t next_full_bar,
+                                                           uint32_t next_parity) {
   uint32_t next_ready;
   if constexpr (G == 1) {
     asm volatile(
         "{\n"
-        ".reg .pred pn;\n"
+        ".reg .pred pn, pa;\n"
         ".reg .b64 a1, a2, a3, b1, b2, b3, c1, c2, c3;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 pn, [%9], %10;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 pn, [%10], %11;\n"
+        "setp.ne.b32 pa, %8, 0;\n"
         "add.u64 a1, %3, 2;\n"
         "add.u64 a2, %3, 4;\n"
         "add.u64 a3, %3, 6;\n"
@@ -444,28 +446,29 @@ __device__ __forceinline__ uint32_t umma_kstep8_probe_next(uint32_t d_tmem0, uin
         "add.u64 c1, %5, 2;\n"
         "add.u64 c2, %5, 4;\n"
         "add.u64 c3, %5, 6;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%1], %3, %4, %6, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %3, %4, %6, pa;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%1], a1, b1, %6, 1;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%1], a2, b2, %6, 1;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%1], a3, b3, %6, 1;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%2], %3, %5, %7, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%2], %3, %5, %7, pa;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%2], a1, c1, %7, 1;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%2], a2, c2, %7, 1;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%2], a3, c3, %7, 1;\n"
-        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%8];\n"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%9];\n"
         "selp.u32 %0, 1, 0, pn;\n"
         "}\n"
         : "=r"(next_ready)
         : "r"(d_tmem0), "r"(d_tmem1), "l"(a_desc), "l"(b_desc0), "l"(b_desc1), "r"(idesc0), "r"(idesc1),
-          "r"(commit_bar), "r"(next_full_bar), "r"(next_parity)
+          "r"(accumulate_first), "r"(commit_bar), "r"(next_full_bar), "r"(next_parity)
         : "memory");
   } else {
     asm volatile(
         "{\n"
-        ".reg .pred pn;\n"
+        ".reg .pred pn, pa;\n"
         ".reg .b64 a1, a2, a3, b1, b2, b3, c1, c2, c3;\n"
         ".reg .b16 both;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 pn, [%9], %10;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 pn, [%10], %11;\n"
+        "setp.ne.b32 pa, %8, 0;\n"
         "mov.b16 both, 3;\n"
         "add.u64 a1, %3, 2;\n"
         "add.u64 a2, %3, 4;\n"
@@ -476,20 +479,20 @@ __device__ __forceinline__ uint32_t umma_kstep8_probe_next(uint32_t d_tmem0, uin
         "add.u64 c1, %5, 2;\n"
         "add.u64 c2, %5, 4;\n"
         "add.u64 c3, %5, 6;\n"
-        "tcgen05.mma.cta_group::2.kind::f16 [%1], %3, %4, %6, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %3, %4, %6, pa;\n"
         "tcgen05.mma.cta_group::2.kind::f16 [%1], a1, b1, %6, 1;\n"
         "tcgen05.mma.cta_group::2.kind::f16 [%1], a2, b2, %6, 1;\n"
         "tcgen05.mma.cta_group::2.kind::f16 [%1], a3, b3, %6, 1;\n"
-        "tcgen05.mma.cta_group::2.kind::f16 [%2], %3, %5, %7, 1;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%2], %3, %5, %7, pa;\n"
         "tcgen05.mma.cta_group::2.kind::f16 [%2], a1, c1, %7, 1;\n"
         "tcgen05.mma.cta_group::2.kind::f16 [%2], a2, c2, %7, 1;\n"
         "tcgen05.mma.cta_group::2.kind::f16 [%2], a3, c3, %7, 1;\n"
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], both;\n"
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%9], both;\n"
         "selp.u32 %0, 1, 0, pn;\n"
         "}\n"
         : "=r"(next_ready)
         : "r"(d_tmem0), "r"(d_tmem1), "l"(a_desc), "l"(b_desc0), "l"(b_desc1), "r"(idesc0), "r"(idesc1),
-          "r"(commit_bar), "r"(next_full_bar), "r"(next_parity)
+          "r"(accumulate_first), "r"(commit_bar), "r"(next_full_bar), "r"(next_parity)
         : "memory");
   }
   return next_ready;

@@ -133,6 +133,48 @@ def main() -> None:
         "peer_write": report["peer_write_call_us"] - report["peer_write_kernel_alone_us"],
         "pull": report["pull_call_us"] - report["pull_kernel_alone_us"],
     }
+    # ---- every launch of the reference's two-barrier protocol on its own (GEMM | barrier | copy |
+    # barrier and copy | barrier | GEMM | barrier), whatever protocol the runtime itself uses: what
+    # a barrier kernel and a copy cost on this box next to the GEMMs
+    def launches(steps) -> list[float]:
+        total = args.iters + 3
+        marks = [[torch.cuda.Event(enable_timing=True) for _ in range(len(steps) + 1)] for _ in range(total)]
+        sync_all()
+        for it in range(total):
+            with torch.no_grad(), runtime.lease():
+                marks[it][0].record()
+                for index, step in enumerate(steps):
+                    step()
+                    marks[it][index + 1].record()
+        sync_all()
+        samples = [[m[i].elapsed_time(m[i + 1]) * 1e3 for i in range(len(steps))] for m in marks[3:]]
+        return median_us(samples)
+
+    shard = HIDDEN // up
+    slots = runtime.slots(TOKENS, HIDDEN)
+    stream = lambda: runtime._stream()  # noqa: E731
+
+    def copy_out() -> None:
+        _native.call("mup_gather_rows", out.data_ptr(), slots.data_ptr(), None, up * TOKENS, shard, stream())
+
+    def stage() -> None:
+        _native.call("mup_gather_rows", slots.data_ptr(), hx.data_ptr(), None, up * TOKENS, shard, stream())
+
+    names = ("gemm", "barrier_written", "copy_out", "barrier_reusable")
+    report["peer_write_launches_two_barrier_protocol_us"] = dict(
+        zip(names, launches([lambda: writer.launch(x2d, stream_handle=stream()), runtime.barrier, copy_out, runtime.barrier]))
+    )
+    names = ("staging_copy", "barrier_staged", "pull_gemm", "barrier_reusable")
+
+    def pull_launch() -> None:
+        if puller.compiled.epoch >= puller.compiled.workspace_epochs:
+            puller.compiled.reset_workspace()
+        puller.compiled(stream_handle=stream())
+
+    report["pull_launches_two_barrier_protocol_us"] = dict(
+        zip(names, launches([stage, runtime.barrier, pull_launch, runtime.barrier]))
+    )
+
     # ---- the pull kernel's own trace words over real peers (per CTA; see mup_pull_plan_set_trace)
     sync_all()
     trace = torch.zeros((puller.compiled.grid_ctas, 16), dtype=torch.int64, device=device)

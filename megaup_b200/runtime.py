@@ -48,19 +48,21 @@ _FLAG_TIMEOUT_NS = int(float(os.environ.get("MEGA_UP_FLAG_TIMEOUT_S", "30")) * 1
 _KERNEL_TIMEOUT_NS = int(float(os.environ.get("MEGA_UP_KERNEL_TIMEOUT_S", "5")) * 1e9)
 # How the two slot hand-offs of an operation ("the slots are written" /
 # "the slots may be reused") are carried out, MEGA_UP_HANDOFF:
-#   lazy      (default) one stand-alone barrier kernel per operation for the
-#             first hand-off; the second is only signalled, by the last CTA of
-#             the operation's last kernel, and waited for by the next operation
-#             where it first touches the slots (deep inside its GEMM, or not at
-#             all when the next operation only rewrites this rank's own slots
-#             after reading them itself);
+#   lazy      (default) a peer-write keeps its two stand-alone barrier kernels; a
+#             pull has one (the peers have staged), and its second hand-off
+#             ("I will not read a peer arena again") is only signalled, by the
+#             last pull warp to run out of tickets, long before the GEMM ends;
+#             the next operation waits for it where it first touches the slots:
+#             a peer-write deep inside its GEMM (before its first peer store), a
+#             pull in its staging copy;
 #   folded    both hand-offs ride inside the kernels (no barrier launches);
 #   barriers  two stand-alone barrier kernels per operation (the reference's
 #             protocol, runtime.py:264, :281, :415, :421 there).
-# Measured on 2 B200s, Wan2.1-14B projection, us per step (one peer-write and
-# one pull call): barriers 385, folded 401 (every block of a copy kernel polls
-# system-scope flags, and the GEMM tail has to collect all arrivals before the
-# flags go out).
+# Measured on 2 B200s, Wan2.1-14B projection, us per call (peer-write / pull):
+# barriers 182.8 / 206.2, folded 192.0 / 198.1; with the peer-write's second
+# hand-off signalled from the tail of its copy-out as well 189.1 / 196.8 (a
+# copy kernel that collects arrivals and raises flags is slower than the plain
+# copy plus a barrier kernel).
 _HANDOFF = os.environ.get("MEGA_UP_HANDOFF") or {"1": "folded", "0": "barriers"}.get(
     os.environ.get("MEGA_UP_FUSED_SYNC", ""), "lazy"
 )
@@ -367,15 +369,11 @@ class MegaUPRuntime:
         self._done_value = int(sync.done_after)
 
     def _copy_out_sync(self) -> "_native.MupSync | None":
-        """Hand-off of a copy-out of peer-written slots, after the barrier (if any)
-        this call also issues: folded waits and signals inside the copy, lazy
-        has a barrier kernel in front and only signals from the copy's tail."""
+        """Hand-off folded into a copy-out of peer-written slots (folded protocol
+        only; otherwise barrier kernels stand before and behind the copy)."""
 
         if self.handoff == "folded":
             return self._sync(wait=True, signal=True)
-        if self.handoff == "lazy":
-            self.barrier()
-            return self._sync(wait=False, signal=True)
         return None
 
     def _stage_sync(self) -> "_native.MupSync | None":
@@ -549,7 +547,7 @@ class MegaUPRuntime:
             raise ValueError(
                 f"out must be a contiguous BF16 tensor on the runtime device with shape {expected}"
             )
-        if _managed and self.handoff in ("folded", "lazy"):
+        if _managed and self.handoff == "folded":
             self._regroup(out, self.slots(rows, width), batch, sequence, shard, True, sync=self._copy_out_sync())
             return out
         self.barrier()
@@ -593,7 +591,7 @@ class MegaUPRuntime:
         shard = out.numel() // total
         self.check_capacity(rows, self.up * shard)
         args = (out.data_ptr(), self.slots(rows, self.up * shard).data_ptr(), index.data_ptr(), total, shard)
-        if _managed and self.handoff in ("folded", "lazy"):
+        if _managed and self.handoff == "folded":
             self._copy("mup_gather_rows", *args, sync=self._copy_out_sync())
             return out
         self.barrier()

@@ -83,9 +83,15 @@ def test_items_tile_the_output_exactly_once(rows, n, k, up, mode, cta_group, slo
         assert len(items) > slots
 
 
-def test_headline_shape_uses_wide_items_and_balances_the_rounds() -> None:
+def test_two_accumulator_items_are_chosen_where_they_were_measured_faster() -> None:
+    # K = 8192 (16384 x 8192 x 8192 pull: 10 % faster with 512-wide items), not K = 4096 or 5120
+    assert preview(1, 16384, 8192, 8192, 8, 0, 2, 74)[1] > 256
+    assert preview(0, 4096, 5120, 5120, 8, 0, 2, 74)[1] == 256
+    assert preview(0, 8192, 6144, 4096, 8, 0, 2, 74)[1] == 256
+
+
+def test_headline_shape_balances_the_rounds() -> None:
     items, widest, _ = preview(0, 4096, 5120, 5120, 8, 0, 2, 74)
-    assert widest > 256  # items of two accumulators: one A tile feeds both
     per_slot: dict[int, int] = defaultdict(int)
     for index, entry in enumerate(items):
         if entry != NO_ITEM:
