@@ -34,7 +34,9 @@ if str(ROOT) not in sys.path:
 
 HIDDEN, HEADS, HEAD_DIM, TOKENS = 5120, 40, 128, 4096
 FLOPS_PER_CALL = 2.0 * TOKENS * HIDDEN * HIDDEN
-NVLINK_BYTES_PER_S = 900e9
+# Peer loads from the SMs with every rank reading at once, measured on this pool's
+# B200s (python -m megaup_b200.nvlink_probe; 772 GB/s for a lone reader, 900 nominal).
+NVLINK_BYTES_PER_S = 665e9
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the two GEMM kernels
 # at this shape, from the ncu captures summarised under profiles/ (UP=8, one GPU).
 DRAM_TRAFFIC_BYTES = {"peer_write": 190.2e6 + 31.3e6, "head_shard_pull": 202.9e6 + 73.2e6}
@@ -600,6 +602,7 @@ def main() -> None:
                 "roofline_us": roofline_us,
                 "gemm_us_at_peak": FLOPS_PER_CALL / (burst * 1e12) * 1e6,
                 "nvlink_us": exchanged / NVLINK_BYTES_PER_S * 1e6,
+                "nvlink_gbs_measured": NVLINK_BYTES_PER_S / 1e9,
                 "peer_write_kernel_frac": roofline_us / pw_kernel_us,
                 "pull_kernel_frac": roofline_us / pull_kernel_us,
                 "peer_write_api_frac": roofline_us / pw_api_us,

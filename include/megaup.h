@@ -48,6 +48,7 @@ extern "C" {
 #define MUP_ST_PULL_READY_TIMEOUT 5
 #define MUP_ST_SMEM_MISALIGNED 6
 #define MUP_ST_FLAG_TIMEOUT 7
+#define MUP_ST_ITEM_FEED_TIMEOUT 8
 
 typedef struct mup_peer_write_plan mup_peer_write_plan;
 typedef struct mup_pull_plan mup_pull_plan;

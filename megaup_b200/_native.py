@@ -31,6 +31,7 @@ STATUS_NAMES = {
     5: "TMA producer timed out waiting for pulled rows",
     6: "dynamic shared memory is not 1024-byte aligned",
     7: "slot hand-off flag was not raised by a peer in time",
+    8: "a role timed out waiting for its next work item",
 }
 
 class MupSync(ctypes.Structure):

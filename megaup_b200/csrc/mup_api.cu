@@ -389,21 +389,31 @@ int env_int(const char* name, int fallback) {
   return (env != nullptr && *env) ? atoi(env) : fallback;
 }
 
+// Whether the CTAs (pairs) draw their items from the list as they become free
+// (GemmParams::feed; the list then stays in natural order) or CTA c runs items
+// c, c + grid, ... of a list dealt by balance_rounds. Drawing pays for lists of
+// many rounds (65536 x 5120 x 5120: 2244 against 2270 us; 8192 x 6144 x 4096
+// pull: 296.9 against 299.4 us), where the SMs drift apart; on 4096 x 5120 x
+// 5120 it changes nothing (the slowest CTA pair is the one with a fifth, narrow
+// item either way) and on one-round lists the first draw sits on the critical
+// path (18 -> 25 us). MEGA_UP_ITEM_FEED=0/1 forces it off/on.
+constexpr size_t kFeedMinRounds = 16;
+bool item_feed_enabled(size_t items, int slots) {
+  const int forced = env_int("MEGA_UP_ITEM_FEED", -1);
+  if (forced >= 0) return forced != 0;
+  return items >= kFeedMinRounds * static_cast<size_t>(slots);
+}
+
 struct Schedule {
   std::vector<uint32_t> items;
+  bool fed = false;  // the CTAs draw the items (natural order) instead of a fixed assignment
   int max_cols = 0;
   double critical_cycles = 0;
 };
 
 // Load latency the stages in flight have to cover, in SM cycles (about 1.8 us:
-// every K step touches lines no SM has read in this round of items). While the
-// pull warps of a pull launch keep the memory system busy the operand loads
-// take longer; with 4500 the model picks what was measured on
-// 4096 x 5120 x 5120: 256-wide items for the peer-write kernel (148.5 against
-// 150 us for 512-wide), 512-wide items for the pull kernel (162.7 against
-// 168.3 us).
+// every K step touches lines no SM has read in this round of items).
 constexpr double kModelLoadLatency = 3000.0;
-constexpr double kModelLoadLatencyWhilePulling = 4500.0;
 
 // What the time model needs to know beside an item's width.
 struct ModelShape {
@@ -452,8 +462,20 @@ double list_item_cycles(uint32_t e, const ModelShape& shape) {
   return item_cycles(static_cast<int>((e >> 26) & 0x7u) + 1, shape);
 }
 
-double critical_path(const std::vector<uint32_t>& items, int slots, ModelShape shape) {
+// `start_cycles_per_m_tile` (pull mode): a CTA pair cannot start before the rows
+// of its first item have arrived, and rows arrive in ascending order. Lists of
+// wide items spread their first round over twice as many rows: on two and four
+// GPUs the first panel gate then opened after 32-47 us on average instead of
+// 23-26 us and the pull call of 4096 x 5120 x 5120 took 3-8 us longer, although
+// with peers emulated on one GPU (rows arrive at HBM speed) the wide list was
+// 5 us faster.
+double critical_path(const std::vector<uint32_t>& items, int slots, ModelShape shape,
+                     double start_cycles_per_m_tile) {
   std::vector<double> load(static_cast<size_t>(slots), 0.0);
+  if (start_cycles_per_m_tile > 0.0) {
+    for (size_t c = 0; c < static_cast<size_t>(slots) && c < items.size(); ++c)
+      if (items[c] != mup::kNoItem) load[c] = start_cycles_per_m_tile * ((items[c] & 0x3FFFu) + 1u);
+  }
   std::vector<int> last_class(static_cast<size_t>(slots), 0);
   shape.narrow_class = list_uses_narrow_class(items);
   for (size_t i = 0; i < items.size(); ++i) {
@@ -572,9 +594,10 @@ Schedule build_list(const std::vector<int>& q_of_row, const ListOptions& o, int 
   split_last_round(&s.items, o.slots, tail_pieces);
   s.max_cols = 0;
   for (uint32_t e : s.items) s.max_cols = std::max(s.max_cols, (static_cast<int>((e >> 26) & 0x7u) + 1) * mup::kUnit);
-  if (env_int("MEGA_UP_BALANCE", 1) != 0)
+  s.fed = item_feed_enabled(s.items.size(), o.slots);
+  if (env_int("MEGA_UP_BALANCE", 1) != 0 && !s.fed)
     balance_rounds(&s.items, o.slots, o.shape, o.start_cycles_per_m_tile);
-  s.critical_cycles = critical_path(s.items, o.slots, o.shape);
+  s.critical_cycles = critical_path(s.items, o.slots, o.shape, o.start_cycles_per_m_tile);
   return s;
 }
 
@@ -594,7 +617,7 @@ Schedule choose_schedule(int mode, int m_tiles, int n, int k_tiles, int up, int 
   o.slots = slots;
   o.shape.k_tiles = k_tiles;
   o.shape.g = g;
-  o.shape.latency = (mode == mup::MODE_PULL && up > 1) ? kModelLoadLatencyWhilePulling : kModelLoadLatency;
+  o.shape.latency = kModelLoadLatency;
   if (const char* env = getenv("MEGA_UP_MODEL_LATENCY")) o.shape.latency = atof(env);
   const int units = o.units;
   const int max_units = mup::max_item_cols(g) / mup::kUnit;
@@ -710,16 +733,21 @@ int finish_core(PlanCore* core, int device, int rows, int n, int k, int up, int 
   p.num_items = static_cast<int>(core->host_items.size());
   p.max_item_cols = schedule.max_cols;
   p.row_len = p.row_base = p.row_extra = 0;
-  // The list lives in device memory for the life of the plan.
+  // The list lives in device memory for the life of the plan, with the two
+  // words of the item feed in front of it (zero between launches).
   const size_t bytes = core->host_items.size() * sizeof(uint32_t);
-  void* table = nullptr;
-  MUP_CUDA(cudaMalloc(&table, bytes));
-  cudaError_t e = cudaMemcpy(table, core->host_items.data(), bytes, cudaMemcpyHostToDevice);
+  constexpr size_t kFeedBytes = 16;
+  void* block = nullptr;
+  MUP_CUDA(cudaMalloc(&block, kFeedBytes + bytes));
+  void* table = static_cast<char*>(block) + kFeedBytes;
+  cudaError_t e = cudaMemset(block, 0, kFeedBytes);
+  if (e == cudaSuccess) e = cudaMemcpy(table, core->host_items.data(), bytes, cudaMemcpyHostToDevice);
   if (e != cudaSuccess) {
-    cudaFree(table);
+    cudaFree(block);
     return fail(MUP_ERR_CUDA, "uploading the work-item list failed: %s", cudaGetErrorString(e));
   }
-  core->device_items = table;
+  p.feed = schedule.fed ? static_cast<unsigned int*>(block) : nullptr;
+  core->device_items = block;
   p.items = static_cast<const uint32_t*>(table);
   if (!list_uses_narrow_class(core->host_items)) p.flags |= mup::kFlagNoNarrowClass;
   if (const char* env = getenv("MEGA_UP_KERNEL_FLAGS")) p.flags ^= static_cast<unsigned int>(atoi(env));
@@ -1412,6 +1440,8 @@ int mup_pull_plan_reset(mup_pull_plan* plan, void* stream) {
   if (plan == nullptr) return fail(MUP_ERR_BAD_ARG, "plan is null");
   MUP_CUDA(cudaMemsetAsync(plan->workspace, 0, plan->workspace_bytes,
                            static_cast<cudaStream_t>(stream)));
+  if (plan->core.params.feed != nullptr)
+    MUP_CUDA(cudaMemsetAsync(plan->core.params.feed, 0, 16, static_cast<cudaStream_t>(stream)));
   plan->launches = 0;
   return MUP_OK;
 }
@@ -1568,7 +1598,6 @@ int mup_pull_gemm_noalloc(int device, int rows, int n, int k, int up, int rank, 
     ModelShape shape;
     shape.k_tiles = p.k_tiles;
     shape.g = g;
-    shape.latency = up > 1 ? kModelLoadLatencyWhilePulling : kModelLoadLatency;
     for (int q = q_min; q <= units; ++q) {
       const long long rounds = (static_cast<long long>(m_tiles) * q + slots - 1) / slots;
       const double cost = rounds * item_cycles((units + q - 1) / q, shape);

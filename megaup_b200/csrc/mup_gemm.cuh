@@ -71,6 +71,7 @@ constexpr int kNumBMaps = 4;          // W boxes for parts of 64, 128, 192 and 2
 #endif
 constexpr int kPullMaxVecs = MUP_PULL_MAX_VECS;  // 16-byte vectors per pull ticket (one batch of peer loads per warp)
 constexpr int kPullUnroll = kPullMaxVecs / 32;
+constexpr int kFeedDepth = 16;        // entries of the item feed in shared memory (a power of two)
 constexpr int kPullWarps = 6;         // pull workers per CTA (warps 6 .. 6 + kPullWarps - 1)
 constexpr int kPullChunk = 8;         // tickets drawn per atomic
 constexpr int kPullClaimWords = 1024; // one claim word per pull warp of the grid (148 SMs x 6 = 888)
@@ -87,6 +88,7 @@ constexpr uint32_t ST_EPILOGUE_TIMEOUT = 4;
 constexpr uint32_t ST_PULL_READY_TIMEOUT = 5;
 constexpr uint32_t ST_SMEM_MISALIGNED = 6;
 constexpr uint32_t ST_FLAG_TIMEOUT = 7;
+constexpr uint32_t ST_ITEM_FEED_TIMEOUT = 8;
 
 // Shared-memory plan. The widest item of a launch fixes the size and with it
 // the number of pipeline stages, so the layout keeps a fixed 192 KiB stage
@@ -103,7 +105,8 @@ struct GemmCfg {
   static constexpr int kNumBars = 2 * kMaxStages + 2 * kAccStages;
   static constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
   static constexpr int kOffAbort = kOffTmemSlot + 4;
-  static constexpr int kSmemBytes = kOffAbort + 4 + 56;         // small pad
+  static constexpr int kOffFeed = kOffAbort + 4;                // kFeedDepth 64-bit words (item feed)
+  static constexpr int kSmemBytes = kOffFeed + kFeedDepth * 8 + 56;  // small pad
   static constexpr int kUmmaM = kBlockM * G;
 };
 
@@ -158,6 +161,10 @@ struct GemmParams {
   // them row_base + 1 units wide and the rest row_base units.
   const uint32_t* items;
   int num_items;
+  // Item feed (nullptr: CTA (pair) c runs items c, c + grid, ... of the list).
+  // feed[0]: the next list position to hand out; feed[1]: CTAs (pairs) that
+  // have finished. Both are zero between launches: the last one out clears them.
+  unsigned int* feed;
   int row_len, row_base, row_extra;
   int max_item_cols;                 // widest item: fixes the stage size
   // pull mode only
@@ -364,6 +371,42 @@ __device__ __forceinline__ WorkItem decode_entry(uint32_t e) {
   return w;
 }
 
+// Item feed: with GemmParams::feed set, the CTAs (pairs) take their items from
+// the list in the order they become free instead of in a fixed round-robin
+// (the SMs do not run an item equally fast: with a fixed assignment the
+// slowest CTA pair of 4096 x 5120 x 5120 took 3.5-8 % longer than the mean).
+// One thread per CTA pair, the TMA producer of the leader CTA, draws the list
+// position of its next item with an atomic when it starts an item and writes
+// the drawn entry, tagged with the item's ordinal, into a small ring in the
+// shared memory of both CTAs when it starts the next one; the other roles wait
+// for their ordinal to appear. A position past the end of the list (kNoItem)
+// ends every role. The ring needs no "slot free" signal: an entry is
+// overwritten kFeedDepth items later, and the producer cannot be more than
+// four items ahead of the slowest role (the stages hold less than one item,
+// the two accumulators at most two more).
+__device__ __forceinline__ void feed_publish(uint32_t ring_addr, int ordinal, uint32_t entry) {
+  st_relaxed_cluster_smem_u64(ring_addr + 8u * static_cast<uint32_t>(ordinal & (kFeedDepth - 1)),
+                              (static_cast<uint64_t>(static_cast<uint32_t>(ordinal) + 1u) << 32) | entry);
+}
+
+// False when the wait ran out or the CTA is giving up.
+__device__ __forceinline__ bool feed_wait(uint32_t ring, int ordinal, volatile uint32_t* abort_flag,
+                                          uint64_t timeout_ns, uint32_t* entry) {
+  const uint32_t addr = ring + 8u * static_cast<uint32_t>(ordinal & (kFeedDepth - 1));
+  const uint32_t want = static_cast<uint32_t>(ordinal) + 1u;
+  uint64_t v = ld_relaxed_cluster_smem_u64(addr);
+  if (static_cast<uint32_t>(v >> 32) != want) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t polls = 0;
+    do {
+      if ((++polls & 63u) == 0u && (*abort_flag != 0u || globaltimer_ns() - t0 > timeout_ns)) return false;
+      v = ld_relaxed_cluster_smem_u64(addr);
+    } while (static_cast<uint32_t>(v >> 32) != want);
+  }
+  *entry = static_cast<uint32_t>(v);
+  return true;
+}
+
 // WIDE = false is the kernel for lists whose items all have one accumulator (at
 // most 256 columns): the code of the two-accumulator items is compiled out.
 // Merely having that code in the kernel slowed single-accumulator items by
@@ -399,6 +442,21 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     trace[kTraceNsStart] = globaltimer_ns();
   }
   const uint32_t first_entry = item_entry(p, cluster_id);  // the list is written when the plan is made
+  const bool fed = p.feed != nullptr;
+  const uint32_t feed_ring = smem_base + Cfg::kOffFeed;
+  // Entry of this role's next item. Fixed assignment: `ahead` was fetched while
+  // the previous item ran. 1: *entry is item `ordinal`; 0: no more items; -1: the
+  // feed did not deliver in time.
+  auto next_item = [&](int ordinal, int item, uint32_t& ahead, uint32_t* entry) -> int {
+    if (!fed) {
+      if (item >= num_items) return 0;
+      *entry = ahead;
+      ahead = item_entry(p, item + num_clusters);
+      return 1;
+    }
+    if (!feed_wait(feed_ring, ordinal, abort_flag, timeout_ns, entry)) return -1;
+    return *entry == kNoItem ? 0 : 1;
+  };
   // Pull mode: every pull warp claims its pre-assigned first chunk for this
   // launch. The claim words only ever grow (launch ordinals), so the claim may
   // be made before the previous launch of the plan has completed, and its
@@ -423,6 +481,7 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       mbar_init(acc_full_bar(a), 1);
       mbar_init(acc_empty_bar(a), 4 * G);
     }
+    for (int i = 0; i < kFeedDepth; ++i) reinterpret_cast<volatile uint64_t*>(smem + Cfg::kOffFeed)[i] = 0ull;
     fence_mbar_init();
     tma_prefetch_desc(&p.map_a);
 #pragma unroll
@@ -468,10 +527,32 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
       auto advance = [&](uint32_t& s) {
         if (++s == static_cast<uint32_t>(num_stages)) s = 0;
       };
-      uint32_t entry = first_entry;
-      for (int item = cluster_id; item < num_items && ok; item += num_clusters) {
+      // With an item feed the leader CTA's producer is the one that draws.
+      const bool drawer = fed && cta_rank == 0u;
+      const uint32_t feed_ring_peer = (G == 2) ? mapa_cluster(feed_ring, 1) : 0u;
+      auto draw = [&]() -> uint32_t {
+        const unsigned int at = atomicAdd(p.feed, 1u);
+        return at < static_cast<unsigned int>(num_items) ? __ldg(p.items + at) : kNoItem;
+      };
+      uint32_t ahead = drawer ? draw() : first_entry;
+      for (int ordinal = 0, item = cluster_id; ok; ++ordinal, item += num_clusters) {
+        uint32_t entry;
+        if (drawer) {
+          // `ahead` was drawn when the previous item started; everyone else learns of it now
+          entry = ahead;
+          feed_publish(feed_ring, ordinal, entry);
+          if constexpr (G == 2) feed_publish(feed_ring_peer, ordinal, entry);
+          if (entry == kNoItem) break;
+          ahead = draw();
+        } else {
+          const int got = next_item(ordinal, item, ahead, &entry);
+          if (got < 0) {
+            report_status(p, abort_flag, ST_ITEM_FEED_TIMEOUT, static_cast<uint32_t>(ordinal));
+            ok = false;
+          }
+          if (got <= 0) break;
+        }
         const WorkItem w = decode_entry(entry);
-        entry = item_entry(p, item + num_clusters);
         if (w.parts == 0) continue;
         const int panel = w.m_idx * G + static_cast<int>(cta_rank);
         const int a_row0 = panel * kBlockM;
@@ -675,10 +756,16 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     bool first_mma = true;
     long long wait_full = 0, wait_acc = 0;
     int items_run = 0;
-    uint32_t entry = first_entry;
-    for (int item = cluster_id; item < num_items; item += num_clusters, ++items_run) {
+    uint32_t ahead = first_entry;
+    for (int ordinal = 0, item = cluster_id;; ++ordinal, item += num_clusters, ++items_run) {
+      uint32_t entry;
+      const int got = next_item(ordinal, item, ahead, &entry);
+      if (got < 0) {
+        if (lane == 0) report_status(p, abort_flag, ST_ITEM_FEED_TIMEOUT, static_cast<uint32_t>(ordinal));
+        failed = true;
+      }
+      if (got <= 0) break;
       const WorkItem w = decode_entry(entry);
-      entry = item_entry(p, item + num_clusters);
       if (w.parts == 0) continue;
       {
         const int class_cols =
@@ -904,10 +991,16 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     bool ok = true;
     long long epi_wait = 0;
     bool handoff_checked = false;
-    uint32_t entry = first_entry;
-    for (int item = cluster_id; item < num_items && ok; item += num_clusters) {
+    uint32_t ahead = first_entry;
+    for (int ordinal = 0, item = cluster_id; ok; ++ordinal, item += num_clusters) {
+      uint32_t entry;
+      const int got = next_item(ordinal, item, ahead, &entry);
+      if (got < 0) {
+        if (lane == 0) report_status(p, abort_flag, ST_ITEM_FEED_TIMEOUT, static_cast<uint32_t>(ordinal));
+        ok = false;
+      }
+      if (got <= 0) break;
       const WorkItem w = decode_entry(entry);
-      entry = item_entry(p, item + num_clusters);
       if (w.parts == 0) continue;
       const int row0 = (w.m_idx * G + static_cast<int>(cta_rank)) * kBlockM + q * kEpiRows;
       int part_col0 = w.n0;
@@ -1176,6 +1269,15 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc<G>(tmem_base, kTmemCols);
+  }
+  if (fed && threadIdx.x == 0 && cta_rank == 0u) {
+    // This CTA (pair) draws no more. The last one out leaves the feed as the
+    // next launch expects it (a launch starts drawing only after the launch
+    // before it has completed).
+    if (atomicAdd(p.feed + 1, 1u) == static_cast<unsigned int>(num_clusters) - 1u) {
+      p.feed[1] = 0u;
+      p.feed[0] = 0u;
+    }
   }
   if constexpr (MODE == MODE_PEER_WRITE) {
     // Every store of this CTA has completed (bulk wait in the epilogue warps,

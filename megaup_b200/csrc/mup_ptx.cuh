@@ -35,6 +35,17 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   return r;
 }
 
+// 64-bit words in shared memory that one CTA of a cluster writes and the other
+// polls (relaxed, cluster scope: strong accesses, a word is never seen torn).
+__device__ __forceinline__ void st_relaxed_cluster_smem_u64(uint32_t cluster_smem_addr, uint64_t value) {
+  asm volatile("st.relaxed.cluster.shared::cluster.u64 [%0], %1;" ::"r"(cluster_smem_addr), "l"(value) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_relaxed_cluster_smem_u64(uint32_t local_smem_addr) {
+  uint64_t v;
+  asm volatile("ld.relaxed.cluster.shared::cta.u64 %0, [%1];" : "=l"(v) : "r"(local_smem_addr) : "memory");
+  return v;
+}
+
 // One lane of the (fully converged) warp; the same lane every time.
 __device__ __forceinline__ bool elect_one_sync() {
   uint32_t pred;

@@ -124,9 +124,10 @@ def test_pull_kernel(rows, n, k, up, rank, cta_group) -> None:
 
 @pytest.mark.parametrize("rows,n,k,up,rank", [(4096, 5120, 5120, 8, 5), (640, 2304, 1024, 2, 1), (200, 1024, 1040, 8, 3)])
 def test_the_schedule_never_changes_a_bit(rows, n, k, up, rank, monkeypatch) -> None:
-    """Tile width, the half-width items of the last wave and the issue sequence
-    only decide which SM computes which columns when: every K loop stays whole
-    and ascending, so all variants must give identical bits."""
+    """Item width, the cut-up last round, the issue sequence and whether the CTAs
+    draw their items from a feed or have them assigned only decide which SM
+    computes which columns when: every K loop stays whole and ascending, so all
+    variants must give identical bits."""
 
     x = h.seeded((rows, k), 71, ints=False)
     w, b = _weights(n, k, 72, False)
@@ -134,9 +135,14 @@ def test_the_schedule_never_changes_a_bit(rows, n, k, up, rank, monkeypatch) -> 
     peers = [h.seeded((up, rows, n // up), 80 + p, ints=False) for p in range(up)]
     w_pull, b_pull = _weights(n, n, 73, False)
     results = []
-    variants = [{}, {"MEGA_UP_SPLIT_TAIL": "0"}, {"MEGA_UP_TILE_N": "128"}, {"MEGA_UP_TILE_N": "192", "MEGA_UP_KERNEL_FLAGS": "2"}]
+    variants = [
+        {}, {"MEGA_UP_SPLIT_TAIL": "0"}, {"MEGA_UP_ITEM_UNITS": "2"}, {"MEGA_UP_ITEM_UNITS": "3", "MEGA_UP_KERNEL_FLAGS": "2"},
+        {"MEGA_UP_ITEM_UNITS": "8"}, {"MEGA_UP_ITEM_FEED": "1"}, {"MEGA_UP_ITEM_FEED": "1", "MEGA_UP_ITEM_UNITS": "7"},
+        {"MEGA_UP_ITEM_FEED": "0", "MEGA_UP_ITEM_UNITS": "1"},
+    ]
+    names = ("MEGA_UP_SPLIT_TAIL", "MEGA_UP_ITEM_UNITS", "MEGA_UP_KERNEL_FLAGS", "MEGA_UP_ITEM_FEED")
     for env in variants:
-        for name in ("MEGA_UP_SPLIT_TAIL", "MEGA_UP_TILE_N", "MEGA_UP_KERNEL_FLAGS"):
+        for name in names:
             monkeypatch.delenv(name, raising=False)
         for name, value in env.items():
             monkeypatch.setenv(name, value)
