@@ -579,6 +579,28 @@ Schedule build_list(const std::vector<int>& q_of_row, const ListOptions& o, int 
     const int start = o.rotate ? ((o.rank * q + o.up - 1) / o.up) % q : 0;
     emit_row(&rows[m], m, o.units, q, start);
   }
+  if (o.band > 1 && o.rotate && o.up > 1 && env_int("MEGA_UP_BAND_INTERLEAVE", 1) != 0) {
+    // A band walks its columns one after the other, so without this step it would
+    // store to one destination rank for a long stretch (NVLink then sees the
+    // exchange in bursts). Reorder every row so that consecutive items go to
+    // different destinations: the 1st item of every destination's column block
+    // (in rotation order), then the 2nd of each, ...
+    const int shard_units = o.units / o.up;
+    for (int m = 0; m < m_tiles; ++m) {
+      std::vector<uint32_t>& row = rows[m];
+      std::vector<int> seen(static_cast<size_t>(o.up), 0);
+      std::vector<std::pair<int, size_t>> key(row.size());
+      for (size_t j = 0; j < row.size(); ++j) {
+        const int dest = std::min(o.up - 1, static_cast<int>((row[j] >> 14) & 0xFFFu) / shard_units);
+        key[j] = {seen[static_cast<size_t>(dest)]++, j};
+      }
+      std::stable_sort(key.begin(), key.end(),
+                       [](const std::pair<int, size_t>& x, const std::pair<int, size_t>& y) { return x.first < y.first; });
+      std::vector<uint32_t> reordered(row.size());
+      for (size_t j = 0; j < row.size(); ++j) reordered[j] = row[key[j].second];
+      row.swap(reordered);
+    }
+  }
   if (o.band <= 1) {
     for (int m = 0; m < m_tiles; ++m) s.items.insert(s.items.end(), rows[m].begin(), rows[m].end());
   } else {
@@ -586,16 +608,21 @@ Schedule build_list(const std::vector<int>& q_of_row, const ListOptions& o, int 
       const int m1 = std::min(m_tiles, m0 + o.band);
       size_t longest = 0;
       for (int m = m0; m < m1; ++m) longest = std::max(longest, rows[m].size());
-      for (size_t j = 0; j < longest; ++j)
+      // every other band walks its columns backwards (a serpentine): consecutive
+      // bands then share W boxes at the turn
+      const bool backwards = ((m0 / o.band) & 1) != 0;
+      for (size_t jj = 0; jj < longest; ++jj) {
+        const size_t j = backwards ? longest - 1 - jj : jj;
         for (int m = m0; m < m1; ++m)
           if (j < rows[m].size()) s.items.push_back(rows[m][j]);
+      }
     }
   }
   split_last_round(&s.items, o.slots, tail_pieces);
   s.max_cols = 0;
   for (uint32_t e : s.items) s.max_cols = std::max(s.max_cols, (static_cast<int>((e >> 26) & 0x7u) + 1) * mup::kUnit);
   s.fed = item_feed_enabled(s.items.size(), o.slots);
-  if (env_int("MEGA_UP_BALANCE", 1) != 0 && !s.fed)
+  if (env_int("MEGA_UP_BALANCE", 1) != 0 && !s.fed && o.band <= 1)
     balance_rounds(&s.items, o.slots, o.shape, o.start_cycles_per_m_tile);
   s.critical_cycles = critical_path(s.items, o.slots, o.shape, o.start_cycles_per_m_tile);
   return s;
@@ -607,13 +634,19 @@ Schedule choose_schedule(int mode, int m_tiles, int n, int k_tiles, int up, int 
   o.up = up;
   o.rank = rank;
   o.rotate = (mode == mup::MODE_PEER_WRITE);
-  // MEGA_UP_BAND=b makes a peer-write list walk bands of b M tiles column by
-  // column. With emulated peers b = 16 measured 148.9 against 150.7 us for
-  // 4096 x 5120 x 5120 (the CTA pairs of a round share W boxes rather than A
-  // boxes), but over NVLink all CTA pairs then store into the same peer at the
-  // same time and the kernel slowed from 155 to 162 us on two GPUs: row by row
-  // (every round spreads over all destinations) is the default.
-  o.band = o.rotate ? std::max(1, env_int("MEGA_UP_BAND", 1)) : 1;
+  // A peer-write list walks bands of 8 M tiles column by column, every other
+  // band backwards, with consecutive items of a row going to different
+  // destination ranks (MEGA_UP_BAND=b changes the band, 1 = row by row). The
+  // CTA pairs of a round then work on a squarer patch of the output (8 row tiles
+  // x 9 column tiles instead of 3.7 x 20), more operand loads hit L2 (ncu: DRAM
+  // reads 138 MB for such a raster against 190 MB row by row) and a stage comes
+  // back sooner. 4096 x 5120 x 5120, kernel alone: 143.4 against 147.3 us with
+  // emulated peers (cuBLAS 143.6), 150.3 against 152.7 us on two GPUs, 153.9
+  // against 155.7 us on four. Without the alternation of destinations a band
+  // stores to one rank for a long stretch and NVLink sees the exchange in
+  // bursts: 154.3 us and a call 3-5 us slower on two GPUs. Banded lists are
+  // not dealt by balance_rounds (143.4 against 144.7-145.4 us).
+  o.band = o.rotate ? std::max(1, env_int("MEGA_UP_BAND", 8)) : 1;
   o.slots = slots;
   o.shape.k_tiles = k_tiles;
   o.shape.g = g;
@@ -634,29 +667,59 @@ Schedule choose_schedule(int mode, int m_tiles, int n, int k_tiles, int up, int 
           static_cast<double>(mup::kBlockM) * g * k_tiles * mup::kBlockK * 2.0 * (up - 1) / up / pull_bpc;
   }
   const bool may_split = env_int("MEGA_UP_SPLIT_TAIL", 1) != 0;
+  // The list is chosen among row-by-row candidates; a peer-write list may then
+  // be re-ordered into bands (below).
+  ListOptions banded = o;
+  o.band = 1;
   Schedule best;
+  std::vector<int> best_q;
+  int best_pieces = 1;
   bool have = false;
-  auto consider = [&](Schedule&& cand) {
+  // a list as it is, and with its last round cut into 2, 3 and 4 pieces per item
+  auto consider = [&](const std::vector<int>& q_of_row, int pieces) {
+    Schedule cand = build_list(q_of_row, o, pieces);
     if (!have || cand.critical_cycles < best.critical_cycles * 0.999 ||
         (cand.critical_cycles <= best.critical_cycles * 1.001 && cand.items.size() < best.items.size())) {
       best = std::move(cand);
+      best_q = q_of_row;
+      best_pieces = pieces;
       have = true;
     }
   };
-  // a list as it is, and with its last round cut into 2, 3 and 4 pieces per item
   auto consider_with_tails = [&](const std::vector<int>& q_of_row) {
-    consider(build_list(q_of_row, o, 1));
+    consider(q_of_row, 1);
     long long total = 0;
     for (int q : q_of_row) total += q;
     const long long leftover = total % slots;
     if (!may_split || leftover == 0) return;
-    for (int pieces = 2; pieces <= 4 && leftover * pieces <= slots; ++pieces)
-      consider(build_list(q_of_row, o, pieces));
+    for (int pieces = 2; pieces <= 4 && leftover * pieces <= slots; ++pieces) consider(q_of_row, pieces);
+  };
+  // Banding pays when the CTA pairs of a round then work on a clearly smaller
+  // set of operand rows (A rows + W rows in flight; the threshold of 1.3 sits
+  // between the shapes where it measured faster and slower):
+  //   4096 x 5120 x 5120    row by row 144.8 us, banded 142.2   (ratio 1.37)
+  //   8192 x 6144 x 4096               265.4            263.5   (1.57)
+  //   16384 x 8192 x 8192              1440             1405    (1.38)
+  //   65536 x 5120 x 5120              2181             2150    (1.37)
+  //   8192 x 4096 x 4096               168.9            171.6   (1.19)
+  // and only for lists of four rounds or more: with two rounds the even deal
+  // of balance_rounds matters more (2048 x 5120 x 5120: 76.3 us dealt, 82.7 banded).
+  auto maybe_band = [&]() {
+    if (!have || banded.band <= 1 || best.items.size() < 4 * static_cast<size_t>(slots)) return;
+    const bool forced = getenv("MEGA_UP_BAND") != nullptr;
+    const double q = static_cast<double>(best.items.size()) / m_tiles;  // items per row tile
+    const double item_cols = static_cast<double>(n) / q;
+    const double tile_rows = static_cast<double>(mup::kBlockM) * g;
+    const double rows_wide = std::max(1.0, slots / q) * tile_rows + std::min(q, static_cast<double>(slots)) * item_cols;
+    const double band_rows = std::min(banded.band, m_tiles);
+    const double band_wide = band_rows * tile_rows + std::min(q, slots / band_rows) * item_cols;
+    if (forced || rows_wide >= 1.3 * band_wide) best = build_list(best_q, banded, best_pieces);
   };
   auto uniform = [&](int q) { return std::vector<int>(static_cast<size_t>(m_tiles), q); };
   const int forced_units = env_int("MEGA_UP_ITEM_UNITS", 0);
   if (forced_units >= 1 && forced_units <= max_units) {
     consider_with_tails(uniform(std::min(units, (units + forced_units - 1) / forced_units)));
+    maybe_band();
     return best;
   }
   const int forced_rounds = env_int("MEGA_UP_ROUNDS", 0);
@@ -684,6 +747,7 @@ Schedule choose_schedule(int mode, int m_tiles, int n, int k_tiles, int up, int 
     consider_with_tails(q_of_row);
     if (q_lo >= units) break;
   }
+  maybe_band();
   return best;
 }
 

@@ -129,3 +129,34 @@ def test_bad_schedule_arguments_are_rejected() -> None:
         preview(0, 4096, 5000, 5120, 8, 0, 2, 74)
     with pytest.raises(_native.NativeError):
         preview(0, 4096, 5120, 5120, 8, 8, 2, 74)
+
+
+def test_long_lists_stay_in_list_order_for_the_item_feed() -> None:
+    # 16 rounds or more: the CTA pairs draw the items as they become free, so the
+    # list is not dealt round by round (no placeholders; a pull list has its row
+    # tiles ascending)
+    items, _, _ = preview(1, 65536, 5120, 5120, 8, 0, 2, 74)
+    assert len(items) >= 16 * 74
+    assert NO_ITEM not in items
+    rows = [decode(entry)[0] for entry in items]
+    assert rows[: len(rows) - 74] == sorted(rows[: len(rows) - 74])
+    assert NO_ITEM not in preview(0, 65536, 5120, 5120, 8, 0, 2, 74)[0]
+    # a short pull list is dealt: the headline shape's partly filled last round has placeholders
+    items, _, _ = preview(1, 4096, 5120, 5120, 8, 0, 2, 74)
+    assert NO_ITEM in items
+
+
+def test_peer_write_lists_walk_bands_of_row_tiles_and_alternate_destinations() -> None:
+    up, shard_units = 8, 5120 // 64 // 8
+    items, _, _ = preview(0, 4096, 5120, 5120, up, 3, 2, 74)
+    assert NO_ITEM not in items
+    decoded = [decode(entry) for entry in items]
+    # the first 8 items are one column position of the 8 row tiles of the first band
+    assert [d[0] for d in decoded[:8]] == list(range(8))
+    assert len({d[1] for d in decoded[:8]}) == 1
+    # the rank starts at its own column block, and the next column position goes elsewhere
+    assert decoded[0][1] // shard_units == 3
+    assert decoded[8][1] // shard_units != 3
+    # the second band (row tiles 8..15) follows the first
+    first_of_second_band = next(i for i, d in enumerate(decoded) if d[0] >= 8)
+    assert all(d[0] < 8 for d in decoded[:first_of_second_band])
