@@ -59,8 +59,8 @@ _KERNEL_TIMEOUT_NS = int(float(os.environ.get("MEGA_UP_KERNEL_TIMEOUT_S", "5")) 
 #   barriers  two stand-alone barrier kernels per operation (the reference's
 #             protocol, runtime.py:264, :281, :415, :421 there).
 # Measured on B200s, Wan2.1-14B projection, us per call (peer-write / pull):
-# two GPUs lazy 175.7 / 191.8, barriers 175.4 / 194.9; four GPUs lazy 179.0 /
-# 204.0, barriers 181.0 / 209.2. With an earlier kernel revision on two GPUs:
+# two GPUs lazy 172.3 / 191.3, barriers 172.6 / 191.9; four GPUs lazy 179.4 /
+# 195.4, barriers 179.0 / 196.9. With an earlier kernel revision on two GPUs:
 # barriers 182.8 / 206.2, folded 192.0 / 198.1, and with the peer-write's second
 # hand-off signalled from the tail of its copy-out as well 189.1 / 196.8 (a
 # copy kernel that collects arrivals and raises flags is slower than the plain
