@@ -39,7 +39,7 @@ FLOPS_PER_CALL = 2.0 * TOKENS * HIDDEN * HIDDEN
 NVLINK_BYTES_PER_S = 665e9
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the two GEMM kernels
 # at this shape, from the ncu captures summarised under profiles/ (UP=8, one GPU).
-DRAM_TRAFFIC_BYTES = {"peer_write": 190.2e6 + 31.3e6, "head_shard_pull": 202.9e6 + 73.2e6}
+DRAM_TRAFFIC_BYTES = {"peer_write": 190.2e6 + 31.8e6, "head_shard_pull": 218.7e6 + 73.3e6}
 
 
 def measured_peaks() -> tuple[dict, str]:

@@ -28,7 +28,7 @@ import torch.nn.functional as F
 import megaup_b200 as mega_up
 from megaup_b200.kernels import peer_write_gemm
 
-NVLINK_BYTES_PER_S = 900e9
+NVLINK_BYTES_PER_S = 665e9  # measured: peer loads with every rank reading at once (nvlink_probe)
 
 # name -> (direction, layout, rows-defining dims, N, K, head_dim, bias, scale of W, only_up)
 CONFIGS = {
