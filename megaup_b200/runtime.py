@@ -278,11 +278,14 @@ class MegaUPRuntime:
     _status: _StatusWord | None = field(default=None, repr=False)
     _epoch: int = field(default=0, init=False, repr=False)
     _done_counter: Tensor | None = field(default=None, init=False, repr=False)
+    _flag_array: object = field(default=None, init=False, repr=False)
     _done_value: int = field(default=0, init=False, repr=False)
     _leased: bool = field(default=False, init=False, repr=False)
     _leased_stream: int | None = field(default=None, init=False, repr=False)
     _lease_lock: threading.Lock = field(default_factory=threading.Lock, init=False, repr=False)
     _completion_event: torch.cuda.Event | None = field(default=None, init=False, repr=False)
+    _completion_stream: int | None = field(default=None, init=False, repr=False)
+    _spare_event: torch.cuda.Event | None = field(default=None, init=False, repr=False)
     # device-side failures observed so far; pull executables compare it with the
     # count they last saw and zero their counters after a failure
     failure_count: int = field(default=0, init=False, repr=False)
@@ -336,7 +339,7 @@ class MegaUPRuntime:
 
         if self._done_counter is None:
             self._done_counter = torch.zeros(1, dtype=torch.int64, device=self.device)
-        self._flag_array = _native.pointer_array(self._flag_addresses)
+        self._peer_flag_array()
         sync = _native.MupSync(
             peer_flags=self._flag_array,
             up=self.up,
@@ -352,6 +355,13 @@ class MegaUPRuntime:
         if signal:
             self._epoch += 1
         return sync
+
+    def _peer_flag_array(self) -> object:
+        """The peers' flag addresses as a C array, built once."""
+
+        if self._flag_array is None:
+            self._flag_array = _native.pointer_array(self._flag_addresses)
+        return self._flag_array
 
     def _next_handoff(self) -> "_native.MupSync":
         """Folded protocol: the next kernel of an operation waits for the sync point
@@ -422,25 +432,32 @@ class MegaUPRuntime:
 
         self.check_status()
         stream = torch.cuda.current_stream(self.device)
+        handle = stream.cuda_stream
         with self._lease_lock:
             if self._leased:
                 raise RuntimeError(
                     "Mega-UP arena was re-entered before the previous operation completed"
                 )
             self._leased = True
-            previous = self._completion_event
-        if previous is not None:
+            previous, previous_stream = self._completion_event, self._completion_stream
+        # the same stream orders the operations by itself
+        if previous is not None and previous_stream != handle:
             stream.wait_event(previous)
-        self._leased_stream = stream.cuda_stream
+        self._leased_stream = handle
         try:
             yield self
             self.check_status()
         finally:
             self._leased_stream = None
-            done = torch.cuda.Event()
+            # Two event objects take turns: a wait enqueued on the one recorded by
+            # the previous operation keeps referring to that record, so the other
+            # one can be recorded again now.
+            done = self._spare_event or torch.cuda.Event()
             done.record(stream)
             with self._lease_lock:
+                self._spare_event = self._completion_event
                 self._completion_event = done
+                self._completion_stream = handle
                 self._leased = False
 
     def barrier(self, *, timeout_s: float | None = None) -> None:
@@ -456,7 +473,7 @@ class MegaUPRuntime:
         self._epoch += 1
         _native.call(
             "mup_flag_barrier",
-            _native.pointer_array(self._flag_addresses),
+            self._peer_flag_array(),
             self.up,
             self.local_rank,
             _wire_epoch(self._epoch),
