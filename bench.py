@@ -65,10 +65,36 @@ class ClockSampler:
     def __init__(self, index: int) -> None:
         self.index = index
         self.samples: list[list[str]] = []
+        self.source = "none"
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
 
     def _run(self) -> None:
+        # NVML in this process (what nvidia-smi reads; read-only) takes well under a
+        # millisecond per sample; spawning nvidia-smi takes 0.2-0.7 s on an 8-GPU
+        # box, which left 3 samples in a 2 s region. nvidia-smi is the fallback.
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            names = ("HwSlowdown", "HwThermalSlowdown", "SwThermalSlowdown", "SwPowerCap")
+            masks = [getattr(pynvml, "nvmlClocksThrottleReason" + n, 0) or getattr(pynvml, "nvmlClocksEventReason" + n, 0)
+                     for n in names]
+            self.source = "nvml"
+            while not self._stop.is_set():
+                sm = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                top = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                try:
+                    word = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                except Exception:  # noqa: BLE001 - older bindings
+                    word = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.samples.append([str(sm), str(top)] + ["Active" if word & m else "Not Active" for m in masks])
+                self._stop.wait(0.05)
+            return
+        except Exception:  # noqa: BLE001 - fall back to the command-line tool
+            pass
+        self.source = "nvidia-smi"
         while not self._stop.is_set():
             try:
                 out = subprocess.run(
@@ -102,6 +128,7 @@ class ClockSampler:
             "sm_max_mhz": max(maxima) if maxima else None,
             "reasons": reasons,
             "samples": len(clocks),
+            "source": self.source,
         }
 
 
