@@ -161,6 +161,9 @@ void set_pull_geometry(mup::GemmParams& p, int rows) {
   p.total_tickets = groups * p.up * p.pull_segs;
   p.pull_up_shift = 0;
   while ((1 << p.pull_up_shift) < p.up) ++p.pull_up_shift;
+  p.pull_pace_ns = 0;
+  if (const char* env = getenv("MEGA_UP_PULL_PACE_NS")) p.pull_pace_ns = static_cast<unsigned int>(std::max(0, atoi(env)));
+  if (p.pull_pace_ns > 100u) p.pull_pace_ns = 100u;  // at most 0.1 ms for the last warp of a grid
   p.pull_panel_shift = 0;
   while ((p.pull_rows << p.pull_panel_shift) < mup::kBlockM) ++p.pull_panel_shift;
 }

@@ -183,6 +183,7 @@ struct GemmParams {
   int pull_seg_vecs;                 // 16-byte vectors per segment
   int pull_up_shift;                 // log2(up)
   int pull_panel_shift;              // log2(128 / pull_rows)
+  unsigned int pull_pace_ns;         // the i-th pull warp of the grid issues its first ticket i * pace ns late (0: at once)
   unsigned int flags;                // tuning switches (kFlag*)
   unsigned long long* trace;         // optional [grid][16] cycle counters (nullptr: off)
   SyncParams sync;                   // slot hand-off folded into this launch (flags[0] == nullptr: none)
@@ -1165,6 +1166,17 @@ fused_exchange_gemm_kernel(const __grid_constant__ GemmParams p) {
         const bool handed = sync_wait_warp(p.sync, lane);
         if (!handed && lane == 0) *abort_flag = 1u;
         __syncwarp();
+      }
+      // Every pull warp of the grid would issue its first ticket in the same
+      // microsecond, and the link would deliver that first wave (7 MB) in no
+      // particular order, all of it at about the same time. Pacing the first
+      // tickets at about the rate the link delivers them makes them arrive in
+      // ticket order, so the first panels complete first.
+      if (p.pull_pace_ns != 0u) {
+        const unsigned long long until =
+            globaltimer_ns() + (static_cast<unsigned long long>(blockIdx.x) * kPullWarps + (warp - 6)) * p.pull_pace_ns;
+        while (globaltimer_ns() < until) {
+        }
       }
       int pending_panel = -1;
       int tickets_done = 0;
