@@ -138,9 +138,11 @@ def test_the_schedule_never_changes_a_bit(rows, n, k, up, rank, monkeypatch) -> 
     variants = [
         {}, {"MEGA_UP_SPLIT_TAIL": "0"}, {"MEGA_UP_ITEM_UNITS": "2"}, {"MEGA_UP_ITEM_UNITS": "3", "MEGA_UP_KERNEL_FLAGS": "2"},
         {"MEGA_UP_ITEM_UNITS": "8"}, {"MEGA_UP_ITEM_FEED": "1"}, {"MEGA_UP_ITEM_FEED": "1", "MEGA_UP_ITEM_UNITS": "7"},
-        {"MEGA_UP_ITEM_FEED": "0", "MEGA_UP_ITEM_UNITS": "1"},
+        {"MEGA_UP_ITEM_FEED": "0", "MEGA_UP_ITEM_UNITS": "1"}, {"MEGA_UP_BAND": "1"}, {"MEGA_UP_BAND": "4", "MEGA_UP_BAND_INTERLEAVE": "0"},
+        {"MEGA_UP_PULL_PACE_NS": "5"},
     ]
-    names = ("MEGA_UP_SPLIT_TAIL", "MEGA_UP_ITEM_UNITS", "MEGA_UP_KERNEL_FLAGS", "MEGA_UP_ITEM_FEED")
+    names = ("MEGA_UP_SPLIT_TAIL", "MEGA_UP_ITEM_UNITS", "MEGA_UP_KERNEL_FLAGS", "MEGA_UP_ITEM_FEED", "MEGA_UP_BAND",
+             "MEGA_UP_BAND_INTERLEAVE", "MEGA_UP_PULL_PACE_NS")
     for env in variants:
         for name in names:
             monkeypatch.delenv(name, raising=False)
