@@ -72,7 +72,10 @@ constexpr int kNumBMaps = 4;          // W boxes for parts of 64, 128, 192 and 2
 constexpr int kPullMaxVecs = MUP_PULL_MAX_VECS;  // 16-byte vectors per pull ticket (one batch of peer loads per warp)
 constexpr int kPullUnroll = kPullMaxVecs / 32;
 constexpr int kFeedDepth = 16;        // entries of the item feed in shared memory (a power of two)
-constexpr int kPullWarps = 6;         // pull workers per CTA (warps 6 .. 6 + kPullWarps - 1)
+#ifndef MUP_PULL_WARPS
+#define MUP_PULL_WARPS 6
+#endif
+constexpr int kPullWarps = MUP_PULL_WARPS;  // pull workers per CTA (warps 6 .. 6 + kPullWarps - 1)
 constexpr int kPullChunk = 8;         // tickets drawn per atomic
 constexpr int kPullClaimWords = 1024; // one claim word per pull warp of the grid (148 SMs x 6 = 888)
 
