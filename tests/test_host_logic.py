@@ -309,3 +309,30 @@ def test_secondary_surface_of_the_kernel_modules() -> None:
     assert pull._pull_column_chunks(640, 8) == 2  # eight rows of 640 need two segments of 320
     with pytest.raises(ValueError):
         pull._select_pull_elements_per_lane(100)
+
+
+def test_sync_points_skip_zero_when_the_32_bit_count_wraps() -> None:
+    # 0 means "no wait / no signal" in a kernel's hand-off description, so the
+    # wire value of a sync point is never 0 and stays strictly ordered by
+    # signed distance across the wrap
+    from megaup_b200.runtime import _wire_epoch
+
+    assert _wire_epoch(0) == 0
+    assert [_wire_epoch(c) for c in (1, 2, 3)] == [1, 2, 3]
+    top = 0xFFFFFFFF
+    around = [_wire_epoch(c) for c in range(top - 2, top + 4)]
+    assert 0 not in around
+    assert around == [top - 2, top - 1, top, 1, 2, 3]
+    for earlier, later in zip(around, around[1:]):
+        distance = (later - earlier) & 0xFFFFFFFF
+        assert 0 < distance < 0x80000000  # "later" is ahead of "earlier" as the kernels compare them
+
+
+def test_the_hand_off_protocol_is_validated_on_import() -> None:
+    import subprocess
+    import sys
+
+    code = "import os; os.environ['MEGA_UP_HANDOFF']='sometimes'; import megaup_b200.runtime"
+    repo = Path(__file__).resolve().parent.parent
+    result = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=str(repo))
+    assert result.returncode != 0 and "MEGA_UP_HANDOFF must be lazy, folded or barriers" in result.stderr
