@@ -352,7 +352,8 @@ int check_common(int device, int rows, int n, int k, int up, int rank, const voi
 // ---------------------------------------------------------------- schedule
 //
 // The output is cut into work items of 128*G rows by 64..512 columns; CTA
-// (pair) c runs items c, c + slots, ... of the list built here. Candidate lists
+// (pair) c runs items c, c + slots, ... of the list built here (or, for long
+// lists, draws them in list order: item_feed_enabled). Candidate lists
 // are rated with a time model calibrated on B200 (SM cycles at 1.6-1.7 GHz,
 // 4096 x 5120 x 5120, CTA pairs). One K step of an item of `cols` columns costs
 //
@@ -377,15 +378,19 @@ int check_common(int device, int rows, int n, int k, int up, int rank, const voi
 // with the shortest critical path under round-robin assignment wins. Inside
 // every round after the first the items are then dealt so that the CTA (pair)
 // with the most work so far receives the cheapest item (`kNoItem` entries mark
-// the pairs that sit out a partly filled last round).
+// the pairs that sit out a partly filled last round). A peer-write list of four
+// rounds or more may instead be re-ordered into bands of M tiles (maybe_band in
+// choose_schedule).
 // Measured and rejected: asking L2 for the boxes of later K steps with
 // cp.async.bulk.prefetch.tensor from the TMA producer, 4 to 24 K steps ahead,
 // by every CTA or by one CTA per line: the kernel went from 151 to 196-207 us
 // (the MMA warp then waits for operands 3.5 times as long).
 // Tuning overrides (environment): MEGA_UP_ITEM_UNITS=u forces items of u*64
 // columns, MEGA_UP_ROUNDS=r forces the number of rounds, MEGA_UP_SPLIT_TAIL=0
-// keeps the last round whole, MEGA_UP_BAND=b lists the items of b consecutive
-// M tiles column by column (peer-write only).
+// keeps the last round whole, MEGA_UP_BALANCE=0 keeps list order, MEGA_UP_BAND=b
+// forces bands of b M tiles (peer-write only; 1 = row by row),
+// MEGA_UP_BAND_INTERLEAVE=0 keeps a band's columns in order, MEGA_UP_ITEM_FEED=0/1
+// forces the fixed assignment / the item feed.
 
 int env_int(const char* name, int fallback) {
   const char* env = getenv(name);
