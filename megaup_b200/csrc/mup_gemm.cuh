@@ -11,7 +11,8 @@
 //
 // Work items. The output is cut into items of 128*G rows by 64..512 columns
 // (a multiple of 64), listed by the host in the order they are consumed; CTA
-// (pair) c runs items c, c + #clusters, ... . An item wider than 256 columns is
+// (pair) c runs items c, c + #clusters, ... , or the CTAs draw the items from
+// the list as they become free (the item feed, below). An item wider than 256 columns is
 // computed as two parts that share every A tile: each K step loads A once and
 // feeds it to two accumulators, so a 512-wide item moves 48 KiB per CTA and
 // 1024 tensor cycles where two 256-wide tiles move 64 KiB. On this GPU the
@@ -19,8 +20,10 @@
 // pipe, bounds 256-wide tiles at full clock; wide items bring the demand under
 // that limit. A part is one accumulator of at most 256 FP32 columns in TMEM;
 // the two 256-column halves of TMEM form a ring of accumulator slots that the
-// parts of consecutive items take in turn, so the epilogue of one part overlaps
-// the K loop of the next.
+// parts of consecutive items take in turn, so the epilogue of a one-part item
+// overlaps the K loop of the next item. A two-part item owns both slots: the
+// next item's K loop waits for its epilogue, which is why the host uses wide
+// items only for long K (the WIDE = false instantiation has no code for them).
 //
 // G = 1 runs one CTA per item (tcgen05 cta_group::1); G = 2 pairs two CTAs of a
 // cluster on 256 rows (cta_group::2): each CTA loads its own 128 rows of A and
